@@ -391,11 +391,15 @@ class CacheManager:
         for g in self.paged:
             g.sync()
 
-    def view(self, entry, writes: bool = True) -> LayerCache:
+    def view(self, entry, writes: bool = True, borrows=()) -> LayerCache:
+        """``borrows``: pairs (part, other entry) for an entry of several parts: that part of the
+        view is the other entry's, read only."""
         if entry in self._several:
-            return LayerCache(kind="several", writes=writes, parts=tuple(
-                LayerCache(kind="none", writes=False) if e is None else self.view(e, writes)
-                for e in self._several[entry]))
+            parts = [LayerCache(kind="none", writes=False) if e is None else self.view(e, writes)
+                     for e in self._several[entry]]
+            for part, other in borrows:
+                parts[part] = self.view(self._several[other][part], False)
+            return LayerCache(kind="several", writes=writes, parts=tuple(parts))
         if entry not in self._entry:
             return LayerCache(kind="none", writes=False)
         group, index = self._entry[entry]

@@ -9,9 +9,11 @@ from . import sevipel as _sevipel  # registers Sevipel
 from .sevipel import SevipelConfig
 from . import malazen as _malazen  # registers Malazen
 from .malazen import MalazenConfig
+from . import kemirax as _kemirax  # registers Kemirax
+from .kemirax import KemiraxConfig
 
 __all__ = [
-    "ConfigError", "LayerRun", "LayerSpec", "MalazenConfig", "ModelSpec", "PartSpec", "Qwen3Config", "SevipelConfig",
+    "ConfigError", "KemiraxConfig", "LayerRun", "LayerSpec", "MalazenConfig", "ModelSpec", "PartSpec", "Qwen3Config", "SevipelConfig",
     "architecture_name", "config_from_dict", "known_architectures", "load_config",
     "own_tensors", "register_architecture", "tensor_name", "unregister_architecture",
 ]

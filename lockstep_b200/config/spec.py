@@ -68,12 +68,17 @@ class LayerRun:
     False): it then adds nothing to the cache.  ``add_embedding``: the embedding's output for
     the step's tokens is added to the residual stream right before this run (a model that
     passes over some of its layers several times and feeds the embedding in again each time).
+    ``borrows``: pairs (part, entry) for a layer whose cache need has several parts: part
+    ``part`` of this run's cache is not its own but the same part of cache entry ``entry``, which
+    an earlier run wrote, and is only read (a layer that attends over another layer's keys and
+    values but carries a state of its own besides).
     """
 
     layer: int
     cache: int
     writes_cache: bool = True
     add_embedding: bool = False
+    borrows: tuple = ()
 
 
 @dataclass(frozen=True)
@@ -103,6 +108,9 @@ class ModelSpec:
         for run in self.schedule:
             if not 0 <= run.layer < len(self.layers):
                 raise ValueError(f"schedule names layer {run.layer}, the model has {len(self.layers)}")
+            for part, entry in run.borrows:
+                if entry not in writers or entry == run.cache:
+                    raise ValueError(f"a run borrows part {part} of cache entry {entry} before any run wrote it")
             if run.writes_cache:
                 if run.cache in writers:
                     raise ValueError(f"cache entry {run.cache} is written by two runs of the schedule")

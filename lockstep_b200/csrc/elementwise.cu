@@ -95,7 +95,7 @@ template <typename TO, typename TG>
 __global__ void __launch_bounds__(128)
 rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ row_index,
                const TG* __restrict__ gain_all, TO* __restrict__ y, int rows, int width, int src_rows,
-               float eps, int parts, int* err) {
+               float eps, int parts, int64_t x_ld, int* err) {
   ls_dependency_sync();
   constexpr int KEEP = 64;                    // floats a lane keeps: 16 float4
   const int lane = threadIdx.x & 31;
@@ -109,7 +109,8 @@ rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ row_index,
     if (lane == 0) ls_record_fault(err, LS_DEV_ROW_RANGE, r);
     src = 0;
   }
-  const float* xr = x + ((int64_t)src * parts + part) * width;
+  // (x_ld: the source rows' pitch, where the normed columns are the first of a wider row)
+  const float* xr = x + (int64_t)src * x_ld + (int64_t)part * width;
   TO* yr = y + ((int64_t)r * parts + part) * width;
   const TG* gain = gain_all + (int64_t)part * width;
   const bool vec = (width & 3) == 0 && ((uintptr_t)xr & 15) == 0;
@@ -156,16 +157,18 @@ rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ row_index,
 
 LS_API int ls_rmsnorm(const float* x, const int* row_index, const void* gain, int gain_dtype,
                       void* y, int y_dtype, int rows, int row_width, int src_rows, float eps,
-                      int parts, int* err, cudaStream_t stream) {
+                      int parts, int64_t x_ld, int* err, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (parts <= 0 || row_width % parts) return LS_E_SIZE;
+  if (x_ld <= 0) x_ld = row_width;
+  if (x_ld < row_width) return LS_E_SIZE;
   const int width = row_width / parts;
   // few rows: one warp per block, so that the rows spread over the device
   const int warps = (int64_t)rows * parts >= 1024 ? 4 : 1;
   const int blocks = (rows * parts + warps - 1) / warps;
 #define LS_RMS(TO, TG)                                                                          \
   LS_COUNT(LS_K_RMSNORM), ls_launch(rmsnorm_kernel<TO, TG>, blocks, warps * 32, 0, stream, x, row_index, (const TG*)gain, (TO*)y, \
-                                                            rows, width, src_rows, eps, parts, err)
+                                                            rows, width, src_rows, eps, parts, x_ld, err)
   if (y_dtype == LS_F32 && gain_dtype == LS_F32) LS_RMS(float, float);
   else if (y_dtype == LS_F32 && gain_dtype == LS_BF16) LS_RMS(float, __nv_bfloat16);
   else if (y_dtype == LS_BF16 && gain_dtype == LS_F32) LS_RMS(__nv_bfloat16, float);
@@ -548,6 +551,61 @@ LS_API int ls_weighted_sum(float* residual, const float* branches, long long cou
   const int blocks = (int)((count + 255) / 256 < 148 * 16 ? (count + 255) / 256 : 148 * 16);
   LS_COUNT(LS_K_WEIGHTED_SUM);
   ls_launch(weighted_sum_kernel, blocks, 256, 0, stream, residual, branches, (int64_t)count, n, s, bias, width > 0 ? width : 1);
+  return ls_launch_status();
+}
+
+// --------------------------------------------------------------------------
+// The closing kernel of a layer whose sublayers run side by side on one normed row y:
+//   residual[t, c] += sum_b gate_b[t, c] * branch[b, t, c],  gate_b = sigmoid(z[t, b * width + c] + bias[b * width + c])
+// (float32; z the float32 result of the gates' product, or null for no gates), the sum made from
+// zero in the order of the branches and then added to the stream.  With `carry`, the row y[t] of
+// every token that is the last of its request's portion goes to carry[slot[t], :] in float32: what
+// the next step's first token of that request is shifted towards.
+// --------------------------------------------------------------------------
+template <typename TY>
+__global__ void __launch_bounds__(256) gated_sum_kernel(float* __restrict__ residual, const float* __restrict__ branches,
+                                                        int n, const float* __restrict__ z, const float* __restrict__ bias,
+                                                        int tokens, int width, const TY* __restrict__ y,
+                                                        float* __restrict__ carry, int64_t carry_stride,
+                                                        const int* __restrict__ token_slot) {
+  ls_dependency_sync();
+  const int t = blockIdx.x;
+  const int64_t count = (int64_t)tokens * width;
+  for (int c = threadIdx.x; c < width; c += 256) {
+    const int64_t at = (int64_t)t * width + c;
+    float sum = 0.f;
+    for (int b = 0; b < n; ++b) {
+      float v = branches[(int64_t)b * count + at];
+      if (z != nullptr) {
+        const float logit = z[(int64_t)t * n * width + (int64_t)b * width + c] + bias[b * width + c];
+        v = v * (1.0f / (1.0f + expf(-logit)));
+      }
+      sum += v;
+    }
+    residual[at] += sum;
+  }
+  if (carry != nullptr) {
+    const int slot = token_slot[t];
+    if (t + 1 == tokens || token_slot[t + 1] != slot)
+      for (int c = threadIdx.x; c < width; c += 256)
+        carry[(int64_t)slot * carry_stride + c] = ls_to_float<TY>(y[(int64_t)t * width + c]);
+  }
+}
+
+LS_API int ls_gated_sum(float* residual, const float* branches, int n, const float* z, const float* bias, int tokens,
+                        int width, const void* y, int y_dtype, float* carry, long long carry_stride,
+                        const int* token_slot, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (n <= 0 || width <= 0 || (z != nullptr && bias == nullptr)) return LS_E_SIZE;
+  if (carry != nullptr && (y == nullptr || token_slot == nullptr || carry_stride < width)) return LS_E_SIZE;
+  LS_COUNT(LS_K_GATED_SUM);
+  if (y_dtype == LS_F32)
+    ls_launch(gated_sum_kernel<float>, dim3(tokens), dim3(256), 0, stream, residual, branches, n, z, bias, tokens, width,
+              (const float*)y, carry, (int64_t)carry_stride, token_slot);
+  else if (y_dtype == LS_BF16)
+    ls_launch(gated_sum_kernel<__nv_bfloat16>, dim3(tokens), dim3(256), 0, stream, residual, branches, n, z, bias, tokens,
+              width, (const __nv_bfloat16*)y, carry, (int64_t)carry_stride, token_slot);
+  else return LS_E_DTYPE;
   return ls_launch_status();
 }
 

@@ -164,13 +164,17 @@ __global__ void __launch_bounds__(192) experts_tc_kernel(const __grid_constant__
   }
 }
 
-// out[row, :] = x[row_token[row], :] * row_weight[row], rounded to bfloat16 once
+// out[row, :] = x[row_token[row], :] * row_weight[row] (a copy where row_weight is null), rounded to bfloat16 once
 __global__ void __launch_bounds__(256) gather_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ row_token,
                                                      const float* __restrict__ row_weight,
                                                      __nv_bfloat16* __restrict__ out, int width) {
   ls_dependency_sync();
   const int row = blockIdx.x;
   const int64_t src = (int64_t)row_token[row] * width;
+  if (row_weight == nullptr) {
+    for (int c = threadIdx.x; c < width; c += 256) out[(int64_t)row * width + c] = x[src + c];
+    return;
+  }
   const float w = row_weight[row];
   for (int c = threadIdx.x; c < width; c += 256)
     out[(int64_t)row * width + c] = __float2bfloat16_rn(__bfloat162float(x[src + c]) * w);

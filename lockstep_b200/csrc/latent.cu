@@ -21,8 +21,10 @@ namespace {
 constexpr int THREADS = 256;
 
 struct LatentArgs {
-  const void* proj;        // [tokens, ld]: H heads of [d plain ; dr rotated] queries, then [rank ; dr] of the keys' side
+  const void* proj;        // [tokens, ld]: H heads of [d plain ; dr rotated] queries
   int64_t ld;
+  const void* kv;          // [tokens, kv_ld]: [rank ; dr] of the keys' side (null for a layer that writes no cache)
+  int64_t kv_ld;
   void* q_out;             // [tokens, H, D]: this kernel writes columns rank .. D of every head
   void* pages;             // [num_pages, 2, 1, page_size, D]
   const void* gain;        // [rank]
@@ -118,7 +120,7 @@ __global__ void __launch_bounds__(THREADS) latent_finish_kernel(LatentArgs a, in
     if (threadIdx.x == 0) ls_record_fault(err, LS_DEV_PAGE_RANGE, t);
     return;
   }
-  const T* c = row + a.H * qd;
+  const T* c = reinterpret_cast<const T*>(a.kv) + (int64_t)t * a.kv_ld;
   float ss = 0.f;
   for (int i = threadIdx.x; i < a.rank; i += THREADS) {
     const float v = ls_to_float<T>(c[i]);
@@ -220,19 +222,21 @@ __global__ void __launch_bounds__(256) heads_product_kernel(const T* __restrict_
 
 }  // namespace
 
-LS_API int ls_latent_finish(const void* proj, int64_t ld, int dtype, void* q_out, void* pages, const void* gain,
+LS_API int ls_latent_finish(const void* proj, int64_t ld, const void* kv, int64_t kv_ld, int dtype, void* q_out,
+                            void* pages, const void* gain,
                             int gain_dtype, const float* cos_table, const float* sin_table, const int* positions,
                             const int* token_req, const int* block_table, int table_stride, int tokens, int H, int d,
                             int dr, int rank, int D, int page_size, int num_pages, int max_positions, int interleaved,
                             int write_cache, float eps, const void* w_fold, int* err, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (H <= 0 || d <= 0 || dr < 0 || (dr & 1) || rank <= 0 || D < rank + dr) return LS_E_SIZE;
-  if (ld < (int64_t)H * (d + dr) + rank + dr) return LS_E_SIZE;
+  if (ld < (int64_t)H * (d + dr)) return LS_E_SIZE;
   if (gain_dtype != LS_F32 && gain_dtype != LS_BF16) return LS_E_DTYPE;
-  if (write_cache && (pages == nullptr || page_size <= 0)) return LS_E_SIZE;
+  if (write_cache && (pages == nullptr || page_size <= 0 || kv == nullptr || kv_ld < rank + dr || gain == nullptr))
+    return LS_E_SIZE;
   if (dr > 0 && (cos_table == nullptr || sin_table == nullptr)) return LS_E_SIZE;
   LatentArgs a;
-  a.proj = proj; a.ld = ld; a.q_out = q_out; a.pages = pages; a.gain = gain; a.gain_bf16 = gain_dtype == LS_BF16 ? 1 : 0;
+  a.proj = proj; a.ld = ld; a.kv = kv; a.kv_ld = kv_ld; a.q_out = q_out; a.pages = pages; a.gain = gain; a.gain_bf16 = gain_dtype == LS_BF16 ? 1 : 0;
   a.cos_table = cos_table; a.sin_table = sin_table; a.positions = positions; a.token_req = token_req;
   a.block_table = block_table; a.table_stride = table_stride; a.H = H; a.d = d; a.dr = dr; a.rank = rank; a.D = D;
   a.page_size = page_size > 0 ? page_size : 1; a.num_pages = num_pages; a.max_positions = max_positions;

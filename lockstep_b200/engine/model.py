@@ -8,6 +8,8 @@ run is ``spec.schedule``.
 
 from __future__ import annotations
 
+from dataclasses import replace
+
 import torch
 
 from ..config.spec import ModelSpec, own_tensors, tensor_name
@@ -63,10 +65,24 @@ class Model:
         needs = [None] * self.spec.cache_entries
         for run in self.spec.schedule:
             if run.writes_cache:
-                needs[run.cache] = self.blocks[run.layer].cache_need()
+                need = self.blocks[run.layer].cache_need()
+                if run.borrows:
+                    # the borrowed parts are another entry's: this one holds nothing in their place
+                    if need is None or need.kind != "several":
+                        raise ValueError(f"layer {run.layer} borrows a part of a cache need that has no parts")
+                    taken = {part for part, _ in run.borrows}
+                    need = replace(need, parts=tuple(None if i in taken else sub for i, sub in enumerate(need.parts)))
+                needs[run.cache] = need
         for run in self.spec.schedule:
             if not run.writes_cache and needs[run.cache] is not None:
                 needs[run.cache] = needs[run.cache].widened(self.blocks[run.layer].cache_need())
+            for part, entry in run.borrows:
+                reader, lender = self.blocks[run.layer].cache_need().parts[part], needs[entry]
+                if lender is None or lender.kind != "several" or lender.parts[part] is None:
+                    raise ValueError(f"layer {run.layer} borrows part {part} of cache entry {entry}, which has none")
+                parts = list(lender.parts)
+                parts[part] = parts[part].widened(reader)
+                needs[entry] = replace(lender, parts=tuple(parts))
         return needs
 
 

@@ -120,7 +120,7 @@ class ModelRunner:
 
         def layer_step(fn, run):
             def call(h, ctx):
-                fn(h, ctx, self.cache.view(run.cache, run.writes_cache))
+                fn(h, ctx, self.cache.view(run.cache, run.writes_cache, run.borrows))
                 return h
             return call
 

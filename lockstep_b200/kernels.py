@@ -46,7 +46,9 @@ _SIGNATURES = {
     "core": {
         "ls_embed_gather": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
         "ls_rmsnorm": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
-                       c_float, c_int, c_void_p, c_void_p],
+                       c_float, c_int, c_int64, c_void_p, c_void_p],
+        "ls_gated_sum": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p,
+                         ctypes.c_longlong, c_void_p, c_void_p],
         "ls_clamped_glu": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_float,
                            c_void_p, c_void_p, c_int, c_void_p],
         "ls_row_bias": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
@@ -96,7 +98,7 @@ _SIGNATURES["seq"] = {
     "ls_qkv_finish": [c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                       c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                       c_int, c_int, c_float, c_int, c_int, c_int, c_void_p, c_int, c_float, c_int, c_void_p, c_void_p],
-    "ls_latent_finish": [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+    "ls_latent_finish": [c_void_p, c_int64, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                          c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                          c_int, c_float, c_void_p, c_void_p, c_void_p],
     "ls_heads_product": [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_int,
@@ -115,7 +117,9 @@ _SIGNATURES["seq"] = {
                          c_float, c_int64, c_void_p],
     "ls_tanh_rows": [c_void_p, c_int, ctypes.c_longlong, c_void_p],
     "ls_experts_tile_rows": [],
-    "ls_experts_route": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
+    "ls_experts_route": [c_void_p, ctypes.c_longlong, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+    "ls_experts_mix": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
+                       ctypes.c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "ls_experts_plan": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                         c_void_p, c_void_p],
     "ls_experts_tc_tile_rows": [],
@@ -271,13 +275,16 @@ def embed_gather(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, err:
 
 
 def rmsnorm(x: torch.Tensor, gain: torch.Tensor, out: torch.Tensor, eps: float, err: torch.Tensor,
-            row_index: torch.Tensor | None = None, groups: int = 1) -> None:
+            row_index: torch.Tensor | None = None, groups: int = 1, columns: int | None = None) -> None:
     """``groups`` > 1: a row is cut into that many equal consecutive parts, each divided by its
-    own root mean square; the gain runs over the whole row."""
+    own root mean square; the gain runs over the whole row.  ``columns``: only the first so many
+    columns of every row of ``x`` are the row to norm (a part of a wider product's result)."""
     rows, width = out.shape
     if groups < 1 or width % groups:
         raise KernelError(f"rmsnorm: a row of {width} elements cannot be cut into {groups} equal parts")
-    if x.shape[1] != width or gain.numel() != width:
+    if columns is not None and (columns != width or x.shape[1] < width):
+        raise KernelError("rmsnorm: the columns to norm do not match the output")
+    if (columns is None and x.shape[1] != width) or gain.numel() != width:
         raise KernelError("rmsnorm: shapes do not agree")
     if row_index is None and x.shape[0] != rows:
         raise KernelError("rmsnorm: row counts do not agree")
@@ -285,8 +292,29 @@ def rmsnorm(x: torch.Tensor, gain: torch.Tensor, out: torch.Tensor, eps: float, 
         raise KernelError("rmsnorm: row_index does not match the output rows")
     _check(library().ls_rmsnorm(
         _dev(x, "x", torch.float32), _opt(row_index, "row_index", torch.int32), _dev(gain, "gain"),
-        _code(gain), _dev(out, "out"), _code(out), rows, width, x.shape[0], float(eps), int(groups),
+        _code(gain), _dev(out, "out"), _code(out), rows, width, x.shape[0], float(eps), int(groups), x.shape[1],
         _dev(err, "err", torch.int32), _stream()), "rmsnorm")
+
+
+def gated_sum(residual, branches, z, bias, carry=None) -> None:
+    """residual += sum_b sigmoid(z[:, b] + bias[b]) * branches[b]: ``branches`` float32 [n, tokens, width], ``z``
+    float32 [tokens, n * width] and ``bias`` float32 [n * width], or both None for a plain sum.  ``carry`` =
+    (y [tokens, width], state float32 [slots, >= width], token_slot): the row of y of every token that ends its
+    request's portion is kept in ``state[slot]``."""
+    n, tokens, width = branches.shape
+    if tuple(residual.shape) != (tokens, width) or (z is None) != (bias is None):
+        raise KernelError("gated_sum: shapes do not agree")
+    if z is not None and (tuple(z.shape) != (tokens, n * width) or bias.numel() != n * width):
+        raise KernelError("gated_sum: the gates do not match the branches")
+    y, state, token_slot = carry if carry is not None else (None, None, None)
+    if y is not None and (tuple(y.shape) != (tokens, width) or state.dim() != 2 or state.shape[1] < width
+                          or token_slot.numel() != tokens):
+        raise KernelError("gated_sum: the rows to carry do not match")
+    _check(library().ls_gated_sum(
+        _dev(residual, "residual", torch.float32), _dev(branches, "branches", torch.float32), n,
+        _opt(z, "z", torch.float32), _opt(bias, "bias", torch.float32), tokens, width, _opt(y, "y"),
+        _code(y) if y is not None else F32, _opt(state, "state", torch.float32),
+        state.stride(0) if state is not None else 0, _opt(token_slot, "token_slot", torch.int32), _stream()), "gated_sum")
 
 
 def qk_norm_rope_store(qkv, q_out, pages, q_gain, k_gain, cos, sin, positions, token_req,
@@ -687,10 +715,12 @@ def qkv_finish(qkv, q_out, pages, q_gain, k_gain, cos, sin, positions, token_req
 
 
 def latent_finish(proj, q_out, pages, gain, cos, sin, positions, token_req, block_table, heads: int, d: int, dr: int,
-                  rank: int, pad: int, eps: float, interleaved: bool, write_cache: bool, err, w_fold=None) -> None:
+                  rank: int, pad: int, eps: float, interleaved: bool, write_cache: bool, err, w_fold=None,
+                  kv=None) -> None:
     """Between the projections and the attention over a cached latent (csrc/latent.cu).  ``proj`` [tokens, >=
-    heads (d + dr) + rank + dr]: every head's plain and rotated query part, then the latent and the shared
-    rotated key part.  Writes the rotated query parts (and the padding) to columns rank .. pad of every head of
+    heads (d + dr)]: every head's plain and rotated query part; ``kv`` [tokens, >= rank + dr]: the latent and the
+    shared rotated key part (default: the columns of ``proj`` behind the queries; unused when no cache is
+    written).  Writes the rotated query parts (and the padding) to columns rank .. pad of every head of
     ``q_out`` [tokens, heads pad], and [norm(latent) ; rotated key part ; 0] / [norm(latent) ; 0] as the token's
     key and value rows into ``pages`` [num_pages, 2, 1, page_size, pad].  With ``w_fold`` [heads, rank, d] it also
     writes columns 0 .. rank of every head, plain query part @ w_fold[head].T, with the bits of ``heads_product`` (for
@@ -698,16 +728,22 @@ def latent_finish(proj, q_out, pages, gain, cos, sin, positions, token_req, bloc
     tokens = proj.shape[0]
     if w_fold is not None and (tuple(w_fold.shape) != (heads, rank, d) or w_fold.dtype != proj.dtype):
         raise KernelError("latent_finish: the fold's weights do not match")
-    if q_out.shape != (tokens, heads * pad) or q_out.dtype != proj.dtype or gain.numel() != rank:
+    if q_out.shape != (tokens, heads * pad) or q_out.dtype != proj.dtype:
         raise KernelError("latent_finish: shapes do not agree")
+    if write_cache:
+        if kv is None:
+            kv = proj[:, heads * (d + dr):]
+        if kv.shape[0] != tokens or kv.shape[1] < rank + dr or kv.dtype != proj.dtype or gain.numel() != rank:
+            raise KernelError("latent_finish: the latent's columns do not match")
+    kp, kv_ld = _rows(kv, "kv") if write_cache else (0, 0)
     if write_cache and (pages.dtype != proj.dtype or tuple(pages.shape[1:3]) != (2, 1) or pages.shape[4] != pad):
         raise KernelError("latent_finish: cache pages do not match")
     if dr and (cos.shape != sin.shape or cos.shape[1] != dr // 2):
         raise KernelError("latent_finish: rotary tables do not match the rotated part")
     pp, ld = _rows(proj, "proj")
     _check(library("seq").ls_latent_finish(
-        pp, ld, _code(proj), _dev(q_out, "q_out"), _opt(pages if write_cache else None, "pages"), _dev(gain, "gain"),
-        _code(gain), _opt(cos if dr else None, "cos", torch.float32), _opt(sin if dr else None, "sin", torch.float32),
+        pp, ld, kp, kv_ld, _code(proj), _dev(q_out, "q_out"), _opt(pages if write_cache else None, "pages"),
+        _opt(gain if write_cache else None, "gain"), _code(gain) if write_cache else F32, _opt(cos if dr else None, "cos", torch.float32), _opt(sin if dr else None, "sin", torch.float32),
         _dev(positions, "positions", torch.int32), _dev(token_req, "token_req", torch.int32),
         _dev(block_table, "block_table", torch.int32), block_table.shape[-1], tokens, heads, d, dr, rank, pad,
         pages.shape[3] if write_cache else 1, pages.shape[0] if write_cache else 0, cos.shape[0] if dr else 0,
@@ -830,11 +866,40 @@ def experts_tile_rows(tensor_cores: bool = False) -> int:
     return int(lib.ls_experts_tc_tile_rows() if tensor_cores else lib.ls_experts_tile_rows())
 
 
-def experts_route(logits, top: int, ids, weights) -> None:
-    tokens, experts = logits.shape
-    _check(library("seq").ls_experts_route(_dev(logits, "logits", torch.float32), tokens, experts, top,
+def experts_route(logits, top: int, ids, weights, experts: int | None = None, softmax: bool = False,
+                  correction=None) -> None:
+    """The ``top`` experts of every token and their weights, from float32 ``logits`` [tokens, >= experts] (the
+    first ``experts`` columns; default all).  The weight is the sigmoid of the logit, or with ``softmax`` the
+    softmax over the experts; ``correction`` (float32 [experts]) is added to it for the choice alone."""
+    tokens = logits.shape[0]
+    experts = logits.shape[1] if experts is None else int(experts)
+    if correction is not None and correction.numel() != experts:
+        raise KernelError("experts_route: the correction does not match the experts")
+    _check(library("seq").ls_experts_route(_dev(logits, "logits", torch.float32), logits.shape[1], tokens, experts, top,
+                                           1 if softmax else 0, _opt(correction, "correction", torch.float32),
                                            _dev(ids, "ids", torch.int32), _dev(weights, "weights", torch.float32),
                                            _stream()), "experts_route")
+
+
+def experts_mix(y, pair_row, ids, weights, real: int, x, out, shared=None, shared_gate=None, store: bool = False) -> None:
+    """out[t] (+)= sum_r weights[t, r] * (y[pair_row[t, r]] if ids[t, r] < real else x[t]) + sigmoid(shared_gate[t])
+    * shared[t], in order of rank: ids from ``real`` on are identity experts; ``weights`` None counts as one,
+    ``shared`` (float32 [tokens, width]) None as absent, ``shared_gate`` (a float32 column, one logit per token) None
+    as a weight of one.  ``store``: ``out`` is written instead of added to."""
+    tokens, width = out.shape
+    top = ids.shape[1]
+    if x.shape != (tokens, width) or (shared is not None and tuple(shared.shape) != (tokens, width)):
+        raise KernelError("experts_mix: shapes do not agree")
+    gate_ld = 0
+    if shared_gate is not None:
+        if shared_gate.dtype != torch.float32 or shared_gate.shape[0] != tokens or not shared_gate.is_cuda:
+            raise KernelError("experts_mix: the shared expert's gate does not match")
+        gate_ld = shared_gate.stride(0) if tokens > 1 else 1
+    _check(library("seq").ls_experts_mix(
+        _opt(y, "y", torch.float32), _dev(pair_row, "pair_row", torch.int32), _dev(ids, "ids", torch.int32),
+        _opt(weights, "weights", torch.float32), int(real), _dev(x, "x"), _code(x), _opt(shared, "shared", torch.float32),
+        shared_gate.data_ptr() if shared_gate is not None else 0, gate_ld, _dev(out, "out", torch.float32), tokens, top,
+        width, 1 if store else 0, _stream()), "experts_mix")
 
 
 def experts_plan(ids, weights, experts: int, tile_rows: int, plan, max_tiles: int, row_token, row_weight, pair_row,
@@ -849,14 +914,15 @@ def experts_plan(ids, weights, experts: int, tile_rows: int, plan, max_tiles: in
 
 def experts_product(mode: int, plan, max_tiles: int, a, row_token, row_weight, w, c) -> None:
     """mode 0: c[row] = relu((a[row_token[row]] * row_weight[row]) @ w[e].T)^2; mode 1: c[row] = a[row] @ w[e].T
-    in float32; mode 2: c[row_token[row]] += a[row] @ w[e].T (float32; for a token's one expert); rows sorted by
+    in float32; mode 2: c[row_token[row]] += a[row] @ w[e].T (float32; for a token's one expert); mode 3:
+    c[row] = (a[row_token[row]] * row_weight[row]) @ w[e].T in float32 (``row_weight`` None: one); rows sorted by
     expert as ``plan`` says.  w [experts, n, k]."""
     n, k = w.shape[1], w.shape[2]
     if a.shape[1] != k or c.shape[1] != n or a.dtype != w.dtype:
         raise KernelError("experts_product: shapes do not agree")
     _check(library("seq").ls_experts_product(
         mode, _code(a), _dev(plan, "plan", torch.int32), max_tiles, _dev(a, "a"),
-        _dev(row_token, "row_token", torch.int32), _dev(row_weight, "row_weight", torch.float32), _dev(w, "w"),
+        _dev(row_token, "row_token", torch.int32), _opt(row_weight, "row_weight", torch.float32), _dev(w, "w"),
         _dev(c, "c"), n, k, _stream()), "experts_product")
 
 
@@ -868,13 +934,13 @@ def experts_combine(y, pair_row, residual, top: int) -> None:
 
 
 def experts_gather(x, row_token, row_weight, out) -> None:
-    """out[row] = x[row_token[row]] * row_weight[row] (bfloat16): the sorted, scaled rows that the
-    tensor-core product of the experts' first matrices reads."""
+    """out[row] = x[row_token[row]] * row_weight[row] (bfloat16; ``row_weight`` None: a copy): the sorted,
+    scaled rows that the tensor-core product of the experts' first matrices reads."""
     rows, width = out.shape
     if x.shape[1] != width or x.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
         raise KernelError("experts_gather: shapes or types do not agree")
     _check(library("seq").ls_experts_gather(_dev(x, "x"), _dev(row_token, "row_token", torch.int32),
-                                            _dev(row_weight, "row_weight", torch.float32), _dev(out, "out"), rows,
+                                            _opt(row_weight, "row_weight", torch.float32), _dev(out, "out"), rows,
                                             width, _stream()), "experts_gather")
 
 

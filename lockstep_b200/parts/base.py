@@ -186,6 +186,10 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    # True for a feed-forward whose ``forward`` takes ``overwrite=True`` and then stores its result in
+    # ``residual`` (which holds nothing yet) instead of adding it
+    can_overwrite = False
+
     def forward(self, x: torch.Tensor, ctx, residual: torch.Tensor) -> None:
         raise NotImplementedError
 

@@ -2,12 +2,24 @@
 h += mixer(norm_a(h)); h += feed_forward(norm_b(h))  (LockStep: engine/model/qwen3.py:242-287).
 The names under which the layer's tensors are stored are parameters of the
 arrangement, so the same arrangement serves architectures that name them otherwise.
-A layer whose feed-forward is of kind "none" is its mixer alone."""
+A layer whose feed-forward is of kind "none" is its mixer alone.
+
+"shared_norm": one norm feeds the mixer and the feed-forward side by side,
+h += mixer(y) + feed_forward(y) with y = norm(h).  Two options, each with tensors of the layer:
+- ``shift``: the mixer reads y_t + (y_(t-1) - y_t) * mix instead of y_t (``mix`` one number per
+  coordinate; zeros stand for the row before a sequence's first).  The last y of a request is part
+  of what it keeps between steps: the layer's cache need is its mixer's and a state of one row.
+- ``gates``: each sublayer's result is multiplied, coordinate by coordinate, by
+  sigmoid(W y + b) with a matrix and a bias of its own (both gates are one product of y).
+The feed-forward always reads y itself."""
 
 from __future__ import annotations
 
+import torch
+
+from .. import kernels as K
 from ..config.spec import own_tensors, tensor_name
-from .base import Block, Runtime, build_part, register_part
+from .base import Block, CacheNeed, Runtime, WeightSpec, build_part, register_part
 
 _DEFAULT_NAMES = {
     "mixer_norm": "input_layernorm",
@@ -84,3 +96,107 @@ class PreNormBlock(Block):
 @register_part("block", "pre_norm")
 def _build(spec, runtime, layer_spec=None, **_):
     return PreNormBlock(layer_spec, runtime)
+
+
+_SHARED_NAMES = {"norm": "norm", "mixer": "mixer", "feed_forward": "mlp", "shift": "shift",
+                 "mixer_gate": "mixer_gate", "mixer_gate_bias": "mixer_gate.bias",
+                 "feed_forward_gate": "mlp_gate", "feed_forward_gate_bias": "mlp_gate.bias"}
+
+
+class SharedNormBlock(Block):
+    def __init__(self, layer_spec, runtime: Runtime):
+        b = layer_spec.block
+        self.names = dict(_SHARED_NAMES)
+        self.names.update(b.get("names", {}) or {})
+        self.rt, self.width = runtime, int(b["hidden_size"])
+        self.shift, self.gates = bool(b.get("shift", False)), bool(b.get("gates", False))
+        self.position = build_part("position", layer_spec.position, runtime)
+        self.norm = build_part("norm", layer_spec.mixer_norm, runtime)
+        self.mixer = build_part("mixer", layer_spec.mixer, runtime, position=self.position)
+        self.feed_forward = None
+        if layer_spec.feed_forward.kind != "none":
+            self.feed_forward = build_part("feed_forward", layer_spec.feed_forward, runtime)
+        self.mix = self.w_gates = self.b_gates = None
+
+    def _children(self):
+        out = [(self.names["norm"], self.norm), (self.names["mixer"], self.mixer)]
+        if self.feed_forward is not None:
+            out.append((self.names["feed_forward"], self.feed_forward))
+        return out
+
+    def _sublayers(self):
+        return ["mixer"] + (["feed_forward"] if self.feed_forward is not None else [])
+
+    def cache_need(self):
+        need = self.mixer.cache_need()
+        if not self.shift:
+            return need
+        return CacheNeed("several", parts=(need, CacheNeed("state", state_shape=(self.width,),
+                                                           state_dtype=torch.float32)))
+
+    @property
+    def graph_safe(self):
+        return all(part.graph_safe for _, part in self._children()) and self.position.graph_safe
+
+    def attention_windows(self):
+        return set().union(*(part.attention_windows() for _, part in self._children()))
+
+    def weight_specs(self):
+        out, n, w = {}, self.names, self.width
+        for name, part in self._children():
+            for local, spec in part.weight_specs().items():
+                out[tensor_name(name, local)] = spec
+        if self.shift:
+            out[n["shift"]] = WeightSpec((w,), "gain", ("uniform", 0.0, 1.0))
+        if self.gates:
+            for sub in self._sublayers():
+                out[n[sub + "_gate"]] = WeightSpec((w, w))
+                out[n[sub + "_gate_bias"]] = WeightSpec((w,), "gain", ("normal", 0.0, 0.5))
+        return out
+
+    def bind(self, tensors):
+        n = self.names
+        for name, part in self._children():
+            own = own_tensors(name, tensors)
+            if own or part.weight_specs():
+                part.bind(own)
+        if self.shift:
+            self.mix = tensors[n["shift"]].to(torch.float32).reshape(1, self.width).contiguous()
+        if self.gates:
+            subs = self._sublayers()
+            self.w_gates = torch.cat([tensors[n[s + "_gate"]] for s in subs], dim=0).contiguous()
+            self.b_gates = torch.cat([tensors[n[s + "_gate_bias"]] for s in subs]).to(torch.float32).contiguous()
+
+    def forward(self, h, ctx, cache):
+        rt, t, w = self.rt, h.shape[0], self.width
+        y = self.norm.forward(h)
+        mixer_cache, carried = (cache.parts[0], cache.parts[1].state) if self.shift else (cache, None)
+        x = y
+        if self.shift:
+            x = rt.rows(t, w)
+            K.shift_mix(y, self.mix, carried, 0, ctx.token_slot, x.view(1, t, w))
+        subs = self._sublayers()
+        out = rt.rows(len(subs) * t, w, dtype=torch.float32).view(len(subs), t, w)
+        stores = self.mixer.can_overwrite and (self.feed_forward is None or self.feed_forward.can_overwrite)
+        if not stores:
+            K.row_bias(out.view(len(subs) * t, w), None)
+        if stores:
+            self.mixer.forward(x, ctx, mixer_cache, out[0], overwrite=True)
+            if self.feed_forward is not None:
+                self.feed_forward.forward(y, ctx, out[1], overwrite=True)
+        else:
+            self.mixer.forward(x, ctx, mixer_cache, out[0])
+            if self.feed_forward is not None:
+                self.feed_forward.forward(y, ctx, out[1])
+        z = None
+        if self.gates:
+            z = rt.rows(t, len(subs) * w, dtype=torch.float32)
+            K.gemm_nt(y, self.w_gates, z, err=rt.err)
+        # the closing kernel: the (gated) sum into the residual stream, and the last row of every
+        # request's portion into its slot for the next step's shift
+        K.gated_sum(h, out, z, self.b_gates, carry=(y, carried, ctx.token_slot) if self.shift else None)
+
+
+@register_part("block", "shared_norm")
+def _build_shared_norm(spec, runtime, layer_spec=None, **_):
+    return SharedNormBlock(layer_spec, runtime)

@@ -41,15 +41,16 @@ class TokenEmbedding(Part):
 class LinearHead(Part):
     graph_safe = True
 
-    def __init__(self, vocab_size: int, width: int, tied: bool, runtime: Runtime):
+    def __init__(self, vocab_size: int, width: int, tied: bool, runtime: Runtime, tensor: str = "weight"):
         self.vocab, self.width, self.tied, self.rt = int(vocab_size), int(width), bool(tied), runtime
+        self.tensor = str(tensor)     # local name of an untied head's matrix ("" where the part's prefix names it)
         self.weight = None
 
     def weight_specs(self):
-        return {} if self.tied else {"weight": WeightSpec((self.vocab, self.width))}
+        return {} if self.tied else {self.tensor: WeightSpec((self.vocab, self.width))}
 
     def bind(self, tensors):
-        self.weight = tensors["weight"]
+        self.weight = tensors["weight" if self.tied else self.tensor]
 
     def forward(self, y: torch.Tensor) -> torch.Tensor:
         logits = self.rt.rows(y.shape[0], self.vocab, dtype=torch.float32)
@@ -64,4 +65,4 @@ def _build_embedding(spec, runtime, **_):
 
 @register_part("head", "linear_head")
 def _build_head(spec, runtime, **_):
-    return LinearHead(spec["vocab_size"], spec["width"], spec.get("tied", False), runtime)
+    return LinearHead(spec["vocab_size"], spec["width"], spec.get("tied", False), runtime, spec.get("tensor", "weight"))

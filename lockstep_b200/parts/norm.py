@@ -3,7 +3,8 @@
 this number (a tensor that holds the gain minus one: offset 1); the sum is made once, in float32, when the
 weights arrive.  ``tensor``: the local name of the stored tensor ("weight"; "" where the norm's
 own prefix names it).  ``groups`` > 1: the row is cut into that many equal consecutive parts and
-each is divided by its own root mean square (the gain still runs over the whole row)."""
+each is divided by its own root mean square (the gain still runs over the whole row).  ``scalar``:
+the stored gain is one number for all coordinates (a tensor without dimensions)."""
 
 from __future__ import annotations
 
@@ -44,18 +45,22 @@ class RMSNorm(Norm):
     graph_safe = True
 
     def __init__(self, width: int, eps: float, runtime: Runtime, offset: float = 0.0, tensor: str = "weight",
-                 groups: int = 1):
+                 groups: int = 1, scalar: bool = False):
         self.width, self.eps, self.rt = int(width), float(eps), runtime
-        self.offset, self.tensor, self.groups = float(offset), str(tensor), int(groups)
+        self.offset, self.tensor, self.groups, self.scalar = float(offset), str(tensor), int(groups), bool(scalar)
         if self.groups < 1 or self.width % self.groups:
             raise ValueError(f"a norm over {self.width} elements cannot be cut into {self.groups} equal parts")
         self.gain: torch.Tensor | None = None
 
     def weight_specs(self):
-        return {self.tensor: WeightSpec((self.width,), "gain", ("normal", 0.0, 0.1) if self.offset else None)}
+        return {self.tensor: WeightSpec(() if self.scalar else (self.width,), "gain",
+                                        ("normal", 0.0, 0.1) if self.offset else None)}
 
     def bind(self, tensors):
         self.gain = tensors[self.tensor]
+        if self.scalar:
+            # the kernels take a gain per coordinate: the one number, written out once
+            self.gain = self.gain.reshape(1).expand(self.width).contiguous()
         if self.offset:
             self.gain = (self.gain.to(torch.float32) + self.offset).contiguous()
 
@@ -73,4 +78,4 @@ class RMSNorm(Norm):
 @register_part("norm", "rmsnorm")
 def _build(spec, runtime, **_):
     return RMSNorm(spec["width"], spec["eps"], runtime, spec.get("offset", 0.0), spec.get("tensor", "weight"),
-                   spec.get("groups", 1))
+                   spec.get("groups", 1), spec.get("scalar", False))
