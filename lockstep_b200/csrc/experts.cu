@@ -100,10 +100,12 @@ __global__ void __launch_bounds__(PLAN_THREADS) plan_kernel(const int* __restric
                                                             int* __restrict__ row_token,
                                                             float* __restrict__ row_weight, int* __restrict__ pair_row,
                                                             int* err) {
+  // (ids outside 0 .. experts - 1 get no row: the caller's identity experts)
   extern __shared__ int sm[];
   int* count = sm;                  // [experts]
   int* first = count + experts;     // [experts]
   int* cursor = first + experts;    // [experts]
+  __shared__ int sorted_rows;
   ls_dependency_sync();
   const int tid = threadIdx.x;
   for (int e = tid; e < experts; e += PLAN_THREADS) count[e] = cursor[e] = 0;
@@ -127,6 +129,7 @@ __global__ void __launch_bounds__(PLAN_THREADS) plan_kernel(const int* __restric
       }
       at += count[e];
     }
+    sorted_rows = at;
     if (tiles > max_tiles) {
       ls_record_fault(err, LS_DEV_ROW_RANGE, tiles);
       tiles = max_tiles;
@@ -141,6 +144,13 @@ __global__ void __launch_bounds__(PLAN_THREADS) plan_kernel(const int* __restric
     row_token[row] = p / top;
     row_weight[row] = weights[p];
     pair_row[p] = row;
+  }
+  // pairs whose expert has no rows (an identity expert) leave the sorted order shorter than the lists:
+  // the rows past its end name token 0 with the weight zero, so that a kernel that walks all rows of
+  // the lists reads nothing outside the step's tokens
+  for (int row = sorted_rows + tid; row < pairs; row += PLAN_THREADS) {
+    row_token[row] = 0;
+    row_weight[row] = 0.f;
   }
 }
 
