@@ -37,6 +37,11 @@ of an unrecorded step of each with its fraction of the measured peaks.
 bias beside gated linear attention, attention over a cached latent, a clamped gated feed-forward,
 two of the layers run twice) beside Qwen3 layers of equal width, depth, head counts and
 feed-forward size.
+``--workload kemirax`` does the same for the Kemirax design (one norm feeding a mixer behind a token
+shift and routed experts side by side, gates on both; attention over a cached latent with queries
+through a latent and layers that read another layer's cache; gated linear attention; identity and
+shared experts) beside Malazen, the closest design the engine has, at equal width, latent and
+linear head sizes and active feed-forward weights.
 """
 
 from __future__ import annotations
@@ -569,7 +574,7 @@ def kernel_times(runner, entries_of, steps=3):
              "attention_prefill_tc", "attention_combine", "qkv_finish", "find_portions", "delta_prep", "shift_mix",
              "tanh_rows", "double_exp_decay", "state_rule", "head_rms_gate", "experts_route", "experts_plan", "experts_product",
              "experts_product_tc", "experts_gather", "experts_combine", "latent_finish", "heads_product",
-             "sigmoid_power_decay", "clamped_glu", "row_bias", "weighted_sum"]
+             "sigmoid_power_decay", "clamped_glu", "row_bias", "weighted_sum", "gated_sum", "experts_mix"]
     records, saved, graphs = [], {}, runner.graphs
     runner.graphs = None
 
@@ -817,6 +822,163 @@ def run_malazen(args):
     return 0
 
 
+KEMIRAX_SIZES = {
+    "w1024": {"width": 1024, "latent_heads": 8, "linear_heads": 4, "q_rank": 384, "experts": 32, "identity": 4, "top": 4,
+              "expert_ff": 512, "shared_ff": 1024},
+    "w2048": {"width": 2048, "latent_heads": 16, "linear_heads": 8, "q_rank": 768, "experts": 32, "identity": 4, "top": 4,
+              "expert_ff": 1024, "shared_ff": 2048},
+}
+
+
+def kemirax_config(z):
+    """Eight layers: five attend over a cached latent (three of them over another layer's), three are
+    gated linear attention; latent, rotated, plain and value sizes and the linear heads are Malazen's of
+    this file; a token's chosen experts and the shared expert together have the weights of Malazen's
+    dense feed-forward at the same width."""
+    mlp = {"kind": "moe", "expert": {"ff": z["expert_ff"], "limit": 7.0},
+           "router": {"experts": z["experts"], "identity": z["identity"], "top": z["top"]},
+           "shared": {"ff": z["shared_ff"], "limit": 7.0}}
+    lat = {"heads": z["latent_heads"], "dim": MALAZEN_PLAIN, "rot_dim": MALAZEN_ROT, "vdim": MALAZEN_VALUE,
+           "kv_rank": MALAZEN_RANK, "q_rank": z["q_rank"], "scale": (MALAZEN_PLAIN + MALAZEN_ROT) ** -0.5,
+           "rot": {"dims": MALAZEN_ROT, "base": 1000000.0,
+                   "scaling": {"factor": 4.0, "original": 1024, "fast": 32.0, "slow": 1.0}}}
+    gla = {"heads": z["linear_heads"], "dim": 128, "vdim": 128, "tau": 8.0, "decay_rank": 64}
+    kinds = [("latent_attention", lat), ("gla", gla), ("latent_attention", dict(lat, kv_from=0)), ("gla", gla),
+             ("latent_attention", lat), ("latent_attention", dict(lat, kv_from=4)), ("gla", gla),
+             ("latent_attention", dict(lat, kv_from=4))]
+    return {"architecture": "Kemirax", "vocab": DESIGN_VOCAB, "width": z["width"], "norm": {"eps": 1e-5},
+            "max_positions": 4096,
+            "layers": [{"type": t, "mixer": json.loads(json.dumps(m)), "mlp": json.loads(json.dumps(mlp))} for t, m in kinds]}
+
+
+def measure_design(cfg, args, tokens, batch, context):
+    """Prefill and decode times of one configuration, every kernel of an unrecorded step of each."""
+    import torch
+
+    from lockstep_b200 import StepEntry
+
+    engine = build_engine(cfg, "bfloat16", batch, context + 64)
+    runner = engine.runner
+    prefill = time_prefill(runner, tokens)
+    decode = time_decode(runner, engine.sampler, batch, context, 100, args.warmup, repeats=3)
+    ids = [(5 * i + 3) % 1000 for i in range(tokens)]
+
+    def prefill_step(r):
+        runner.open(f"k{r}")
+        runner.step([StepEntry(uid=f"k{r}", tokens=ids, start=0, want=[tokens - 1])], check=False)
+        return lambda: runner.close(f"k{r}")
+
+    def decode_step(r):
+        uids = [f"q{r}_{i}" for i in range(batch)]
+        for u in uids:
+            runner.open(u)
+            runner.fill_random(u, context - 1)
+        runner.step([StepEntry(uid=u, tokens=[7], start=context - 1, want=[0]) for u in uids], check=False)
+        return lambda: [runner.close(u) for u in uids]
+
+    p_kernels, p_launches = kernel_times(runner, prefill_step)
+    d_kernels, d_launches = kernel_times(runner, decode_step)
+    p_ms, d_ms = statistics.median(prefill), statistics.median(decode)
+    del engine, runner
+    torch.cuda.empty_cache()
+    return {"prefill_ms": round(p_ms, 3), "prefill_tok_s": round(tokens / p_ms * 1e3, 1),
+            "decode_ms_per_step": round(d_ms, 4), "decode_tok_s": round(batch / d_ms * 1e3, 1),
+            "prefill_kernels_ms": p_kernels, "prefill_launches": p_launches,
+            "decode_kernels_ms": d_kernels, "decode_launches": d_launches}
+
+
+def run_kemirax(args):
+    pk = peaks()
+    tokens, batch, context = PREFILL_TOKENS, 8, DESIGN_CONTEXT
+    sizes = {}
+    clocks = ClockSampler()
+    clocks.start()
+    for size, z in KEMIRAX_SIZES.items():
+        mz = MALAZEN_SIZES[size]
+        malazen, _ = malazen_configs(mz)
+        row = {"kemirax": measure_design(kemirax_config(z), args, tokens, batch, context),
+               "malazen": measure_design(malazen, args, tokens, batch, context)}
+        k, m = row["kemirax"], row["malazen"]
+        w, QH, LH, qr = z["width"], z["latent_heads"], z["linear_heads"], z["q_rank"]
+        R, DR, DP, DV = MALAZEN_RANK, MALAZEN_ROT, MALAZEN_PLAIN, MALAZEN_VALUE
+        D = -(-(R + DR) // 16) * 16
+        n_lat, n_own, n_gla = 5, 2, 3
+        routed = z["experts"] + z["identity"]
+        # products of a prefill through the engine's product kernels (experts and per-head products apart)
+        lat_cols = qr * w + QH * (DP + DR) * qr + QH * DV * w
+        gla_cols = (4 * LH * 128 + 64) * w + 64 * LH * 128 + LH * 128 * w
+        layer_cols = 2 * w * w + (routed + 1) * w + 3 * z["shared_ff"] * w
+        flops_k = 2 * tokens * (n_lat * lat_cols + n_own * (R + DR) * w + n_gla * gla_cols + 8 * layer_cols) + 2 * DESIGN_VOCAB * w
+        H, G, MLH, MQH, ff = mz["heads"], mz["kv_heads"], mz["linear_heads"], mz["latent_heads"], mz["ff"]
+        par_cols = (H + 2 * G) * 128 + H * 128 + (2 * MLH * 128 + 2 * MLH * 128 + 64) + MLH * 128
+        mlat_cols = MQH * (DP + DR) + R + DR + MQH * DV
+        flops_m = 2 * tokens * (3 * par_cols * w + 5 * mlat_cols * w + 8 * 3 * ff * w) + 2 * DESIGN_VOCAB * w
+        # a token's chosen real experts: top x experts / (experts + identity) on average with random weights
+        real_pairs = tokens * z["top"] * z["experts"] / routed
+        flops_up = 2 * real_pairs * 2 * z["expert_ff"] * w * 8
+        flops_down = 2 * real_pairs * z["expert_ff"] * w * 8
+        pairs_full = tokens * (tokens + 1) // 2
+        pairs_win = sum(min(i + 1, MALAZEN_WINDOW) for i in range(tokens))
+        att_k = n_lat * 4 * pairs_full * QH * D
+        att_m = 3 * 4 * pairs_full * H * 128 + 5 * 4 * pairs_win * MQH * D
+        heads_k = n_lat * 2 * tokens * QH * R * (DP + DV)
+        heads_m = 5 * 2 * tokens * MQH * R * (DP + DV)
+        cache_k = 2 * batch * n_lat * context * 2 * D
+        cache_m = 2 * batch * (3 * context * 2 * G * 128 + 5 * min(context, MALAZEN_WINDOW) * 2 * D)
+        state_k = 2 * 4 * batch * n_gla * LH * 128 * 128
+        state_m = 2 * 4 * batch * 3 * MLH * 128 * 128
+        stream = 4 * tokens * w                     # one float32 pass over the step's rows
+
+        def frac(amount, ms, peak):
+            return round(amount / (ms * 1e-3) / peak, 4) if ms else None
+
+        def ms_of(kernels, *names):
+            return sum(kernels.get(n, 0.0) for n in names)
+
+        tf, bw = pk["bf16_tflops"] * 1e12, pk["hbm_gbs"] * 1e9
+        products = ("gemm_nt_tc", "gemm_nt_tc_rmsnorm")
+        attention = ("attention_tile", "attention_prefill_tc")
+        decode_attention = ("attention_decode", "attention_decode_mma", "attention_tile")
+        row["like_kernels_fraction_of_measured_peak [kemirax, malazen]"] = {
+            "prefill: products (tensor cores)": [frac(flops_k, ms_of(k["prefill_kernels_ms"], *products), tf),
+                                                 frac(flops_m, ms_of(m["prefill_kernels_ms"], *products), tf)],
+            "prefill: attention over the cached latent rows": [
+                frac(att_k, ms_of(k["prefill_kernels_ms"], *attention), tf),
+                frac(att_m, ms_of(m["prefill_kernels_ms"], *attention), tf)],
+            "prefill: per-head products of the latent layers": [
+                frac(heads_k, ms_of(k["prefill_kernels_ms"], "heads_product"), tf),
+                frac(heads_m, ms_of(m["prefill_kernels_ms"], "heads_product"), tf)],
+            "prefill: linear rule, microseconds a token and layer": [
+                round(ms_of(k["prefill_kernels_ms"], "gla_rule") * 1e3 / (n_gla * tokens), 4),
+                round(ms_of(m["prefill_kernels_ms"], "gla_rule") * 1e3 / (3 * tokens), 4)],
+            "prefill: experts' first product (no like kernel in malazen)": [
+                frac(flops_up, ms_of(k["prefill_kernels_ms"], "experts_up"), tf), None],
+            "prefill: experts' second product (no like kernel in malazen)": [
+                frac(flops_down, ms_of(k["prefill_kernels_ms"], "experts_down"), tf), None],
+            "prefill: clamped gated activation (bytes read and written)": [
+                frac(8 * (real_pairs * z["expert_ff"] * (8 + 2) + tokens * z["shared_ff"] * (8 + 2)),
+                     ms_of(k["prefill_kernels_ms"], "clamped_glu"), bw),
+                frac(8 * tokens * ff * (8 + 2), ms_of(m["prefill_kernels_ms"], "clamped_glu"), bw)],
+            "prefill: the layer's closing sum (kemirax: gated_sum, 5 passes over the rows; malazen: weighted_sum, 4)": [
+                frac(8 * 5 * stream, ms_of(k["prefill_kernels_ms"], "gated_sum"), bw),
+                frac(3 * 4 * stream, ms_of(m["prefill_kernels_ms"], "weighted_sum"), bw)],
+            "decode: attention (bytes of cache)": [
+                frac(cache_k, ms_of(k["decode_kernels_ms"], *decode_attention), bw),
+                frac(cache_m, ms_of(m["decode_kernels_ms"], *decode_attention), bw)],
+            "decode: linear rule (bytes of state)": [
+                frac(state_k, ms_of(k["decode_kernels_ms"], "gla_rule"), bw),
+                frac(state_m, ms_of(m["decode_kernels_ms"], "gla_rule"), bw)],
+        }
+        sizes[size] = row
+    clock = clocks.stop()
+    print(json.dumps({
+        "metric": "prefill of 2,048 tokens and decode at batch 8, context 2,048: Kemirax beside Malazen at equal size",
+        "unit": "ms, tok/s", "n_gpus": 1, "dtype": "bf16", "data": "synthetic", "impl": "ours", "clocks": clock,
+        "peaks": pk, "layer_runs": 8, "vocab": DESIGN_VOCAB, "sizes": sizes,
+    }))
+    return 0
+
+
 # ---------------------------------------------------------------------------
 # the reference arm: LockStep itself, unmodified, from baseline/_ref
 # ---------------------------------------------------------------------------
@@ -986,9 +1148,10 @@ def main():
     ap.add_argument("--no-fp32", action="store_true", help="skip the float32 points")
     ap.add_argument("--only", default="", choices=["", "decode", "prefill"],
                     help="time only this part and print a short line (for profiling a small case)")
-    ap.add_argument("--workload", default="decode", choices=["decode", "mixed", "designs", "malazen"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "mixed", "designs", "malazen", "kemirax"],
                     help="mixed: a continuous batch of 64 requests through the entry point; designs: the Sevipel "
-                         "design beside Qwen3 layers of equal size, with every kernel's time")
+                         "design beside Qwen3 layers of equal size, with every kernel's time; malazen, kemirax: the same "
+                         "for those designs")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"],
                     help="element type of the --only runs (the full line always reports both)")
     ap.add_argument("--context", type=int, default=CONTEXT, help="context length of the decode steps (--only decode)")
@@ -1008,6 +1171,8 @@ def main():
         return run_designs(args)
     if args.workload == "malazen":
         return run_malazen(args)
+    if args.workload == "kemirax":
+        return run_kemirax(args)
     return run_ours(args)
 
 
