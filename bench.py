@@ -575,7 +575,7 @@ def kernel_times(runner, entries_of, steps=3):
              "tanh_rows", "double_exp_decay", "state_rule", "head_rms_gate", "experts_route", "experts_plan", "experts_product",
              "experts_product_tc", "experts_gather", "experts_combine", "latent_finish", "heads_product",
              "sigmoid_power_decay", "clamped_glu", "row_bias", "weighted_sum", "gated_sum", "experts_mix"]
-    records, saved, graphs = [], {}, runner.graphs
+    records, saved, graphs, turn = [], {}, runner.graphs, [0]
     runner.graphs = None
 
     def wrap(name, fn):
@@ -584,7 +584,9 @@ def kernel_times(runner, entries_of, steps=3):
             if name == "state_rule":
                 label = {K.RULE_DELTA: "delta_rule", K.RULE_WKV: "wkv_rule", K.RULE_GLA: "gla_rule"}[a[0]]
             elif name in ("experts_product", "experts_product_tc"):
-                label = "experts_up" if a[0] == 0 else "experts_down"
+                # (a feed-forward of experts makes its first product, then its second)
+                turn[0] ^= 1
+                label = "experts_up" if turn[0] else "experts_down"
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
             out = fn(*a, **kw)

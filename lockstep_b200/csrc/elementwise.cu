@@ -434,8 +434,8 @@ LS_API int ls_silu_mul(const void* gate_up, void* out, int dtype, int rows, int 
 // --------------------------------------------------------------------------
 template <typename TI, typename TO, typename TB>
 __global__ void clamped_glu_kernel(const TI* __restrict__ gate_up, const TB* __restrict__ bias, TO* __restrict__ out,
-                                   int64_t rows, int width, float limit, float alpha, float* __restrict__ residual,
-                                   const TB* __restrict__ res_bias, int res_width, int vec) {
+                                   int64_t rows, int width, int64_t in_ld, float limit, float alpha,
+                                   float* __restrict__ residual, const TB* __restrict__ res_bias, int res_width, int vec) {
   ls_dependency_sync();
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   auto act = [&](float g, float u, int c) {
@@ -453,8 +453,8 @@ __global__ void clamped_glu_kernel(const TI* __restrict__ gate_up, const TB* __r
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
       const int64_t r = i / (width >> 2);
       const int c = (int)(i - r * (width >> 2)) << 2;
-      const float4 g4 = ls_load4<TI>(gate_up + r * 2 * width + c);
-      const float4 u4 = ls_load4<TI>(gate_up + r * 2 * width + width + c);
+      const float4 g4 = ls_load4<TI>(gate_up + r * in_ld + c);
+      const float4 u4 = ls_load4<TI>(gate_up + r * in_ld + width + c);
       ls_store4<TO>(out + r * width + c, act(g4.x, u4.x, c), act(g4.y, u4.y, c + 1), act(g4.z, u4.z, c + 2),
                     act(g4.w, u4.w, c + 3));
     }
@@ -463,8 +463,8 @@ __global__ void clamped_glu_kernel(const TI* __restrict__ gate_up, const TB* __r
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
       const int64_t r = i / width;
       const int c = (int)(i - r * width);
-      out[i] = ls_from_float<TO>(act(ls_to_float<TI>(gate_up[r * 2 * width + c]),
-                                     ls_to_float<TI>(gate_up[r * 2 * width + width + c]), c));
+      out[i] = ls_from_float<TO>(act(ls_to_float<TI>(gate_up[r * in_ld + c]),
+                                     ls_to_float<TI>(gate_up[r * in_ld + width + c]), c));
     }
   }
   if (residual != nullptr) {
@@ -474,18 +474,22 @@ __global__ void clamped_glu_kernel(const TI* __restrict__ gate_up, const TB* __r
   }
 }
 
-LS_API int ls_clamped_glu(const void* gate_up, int in_dtype, const void* bias, int bias_dtype, void* out, int out_dtype,
-                          int rows, int width, float limit, float alpha, float* residual, const void* res_bias,
-                          int res_width, cudaStream_t stream) {
+LS_API int ls_clamped_glu(const void* gate_up, long long in_ld, int in_dtype, const void* bias, int bias_dtype, void* out,
+                          int out_dtype, int rows, int width, float limit, float alpha, float* residual,
+                          const void* res_bias, int res_width, cudaStream_t stream) {
   if (rows <= 0) return 0;
-  if (width <= 0 || (residual != nullptr && (res_bias == nullptr || res_width <= 0))) return LS_E_SIZE;
-  const int vec = (width & 3) == 0 && ((uintptr_t)gate_up & 15) == 0 && ((uintptr_t)out & 15) == 0;
+  if (width <= 0 || in_ld < 2 * (long long)width || (residual != nullptr && (res_bias == nullptr || res_width <= 0)))
+    return LS_E_SIZE;
+  // (gate_up may be some columns of a wider row: in_ld is its row pitch in elements)
+  const int in_bytes = in_dtype == LS_F32 ? 4 : 2;
+  const int vec = (width & 3) == 0 && ((uintptr_t)gate_up & 15) == 0 && ((uintptr_t)out & 15) == 0 &&
+                  (in_ld * in_bytes) % 16 == 0;
   const int64_t n = (int64_t)rows * (width / (vec ? 4 : 1) > res_width ? width / (vec ? 4 : 1) : res_width);
   const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
   LS_COUNT(LS_K_CLAMPED_GLU);
 #define LS_GLU(TI, TO, TB)                                                                                        \
   ls_launch(clamped_glu_kernel<TI, TO, TB>, blocks, 256, 0, stream, (const TI*)gate_up, (const TB*)bias, (TO*)out, \
-            (int64_t)rows, width, limit, alpha, residual, (const TB*)res_bias, res_width, vec)
+            (int64_t)rows, width, (int64_t)in_ld, limit, alpha, residual, (const TB*)res_bias, res_width, vec)
   if (in_dtype == LS_F32 && out_dtype == LS_F32 && bias_dtype == LS_F32) LS_GLU(float, float, float);
   else if (in_dtype == LS_F32 && out_dtype == LS_BF16 && bias_dtype == LS_BF16) LS_GLU(float, __nv_bfloat16, __nv_bfloat16);
   else if (in_dtype == LS_F32 && out_dtype == LS_BF16 && bias_dtype == LS_F32) LS_GLU(float, __nv_bfloat16, float);
@@ -562,7 +566,9 @@ LS_API int ls_weighted_sum(float* residual, const float* branches, long long cou
 // every token that is the last of its request's portion goes to carry[slot[t], :] in float32: what
 // the next step's first token of that request is shifted towards.
 // --------------------------------------------------------------------------
-template <typename TY>
+// (VEC = 4: four columns a thread with 16-byte loads, where the width is a multiple of four and every row
+// starts on a 16-byte boundary; the arithmetic of a column is the same.)
+template <typename TY, int VEC>
 __global__ void __launch_bounds__(256) gated_sum_kernel(float* __restrict__ residual, const float* __restrict__ branches,
                                                         int n, const float* __restrict__ z, const float* __restrict__ bias,
                                                         int tokens, int width, const TY* __restrict__ y,
@@ -571,25 +577,66 @@ __global__ void __launch_bounds__(256) gated_sum_kernel(float* __restrict__ resi
   ls_dependency_sync();
   const int t = blockIdx.x;
   const int64_t count = (int64_t)tokens * width;
-  for (int c = threadIdx.x; c < width; c += 256) {
-    const int64_t at = (int64_t)t * width + c;
-    float sum = 0.f;
-    for (int b = 0; b < n; ++b) {
-      float v = branches[(int64_t)b * count + at];
-      if (z != nullptr) {
-        const float logit = z[(int64_t)t * n * width + (int64_t)b * width + c] + bias[b * width + c];
-        v = v * (1.0f / (1.0f + expf(-logit)));
-      }
-      sum += v;
-    }
-    residual[at] += sum;
-  }
+  bool keep = false;
+  int slot = 0;
   if (carry != nullptr) {
-    const int slot = token_slot[t];
-    if (t + 1 == tokens || token_slot[t + 1] != slot)
-      for (int c = threadIdx.x; c < width; c += 256)
-        carry[(int64_t)slot * carry_stride + c] = ls_to_float<TY>(y[(int64_t)t * width + c]);
+    slot = token_slot[t];
+    keep = t + 1 == tokens || token_slot[t + 1] != slot;
   }
+  for (int c = threadIdx.x * VEC; c < width; c += 256 * VEC) {
+    const int64_t at = (int64_t)t * width + c;
+    float sum[VEC];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) sum[i] = 0.f;
+    for (int b = 0; b < n; ++b) {
+      float v[VEC], logit[VEC], add[VEC];
+      if constexpr (VEC == 4) {
+        const float4 q = *reinterpret_cast<const float4*>(branches + (int64_t)b * count + at);
+        v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+      } else {
+        v[0] = branches[(int64_t)b * count + at];
+      }
+      if (z != nullptr) {
+        if constexpr (VEC == 4) {
+          const float4 l = *reinterpret_cast<const float4*>(z + (int64_t)t * n * width + (int64_t)b * width + c);
+          const float4 o = *reinterpret_cast<const float4*>(bias + b * width + c);
+          logit[0] = l.x; logit[1] = l.y; logit[2] = l.z; logit[3] = l.w;
+          add[0] = o.x; add[1] = o.y; add[2] = o.z; add[3] = o.w;
+        } else {
+          logit[0] = z[(int64_t)t * n * width + (int64_t)b * width + c];
+          add[0] = bias[b * width + c];
+        }
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) v[i] = v[i] * (1.0f / (1.0f + expf(-(logit[i] + add[i]))));
+      }
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) sum[i] += v[i];
+    }
+    if constexpr (VEC == 4) {
+      float4 r = *reinterpret_cast<float4*>(residual + at);
+      r.x += sum[0]; r.y += sum[1]; r.z += sum[2]; r.w += sum[3];
+      *reinterpret_cast<float4*>(residual + at) = r;
+    } else {
+      residual[at] += sum[0];
+    }
+    if (keep) {
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) carry[(int64_t)slot * carry_stride + c + i] = ls_to_float<TY>(y[at + i]);
+    }
+  }
+}
+
+template <typename TY>
+static void gated_sum_launch(float* residual, const float* branches, int n, const float* z, const float* bias, int tokens,
+                             int width, const TY* y, float* carry, int64_t carry_stride, const int* token_slot,
+                             cudaStream_t stream) {
+  auto aligned = [](const void* p) { return p == nullptr || (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  if (width % 4 == 0 && aligned(residual) && aligned(branches) && aligned(z) && aligned(bias))
+    ls_launch(gated_sum_kernel<TY, 4>, dim3(tokens), dim3(256), 0, stream, residual, branches, n, z, bias, tokens, width, y,
+              carry, carry_stride, token_slot);
+  else
+    ls_launch(gated_sum_kernel<TY, 1>, dim3(tokens), dim3(256), 0, stream, residual, branches, n, z, bias, tokens, width, y,
+              carry, carry_stride, token_slot);
 }
 
 LS_API int ls_gated_sum(float* residual, const float* branches, int n, const float* z, const float* bias, int tokens,
@@ -600,11 +647,11 @@ LS_API int ls_gated_sum(float* residual, const float* branches, int n, const flo
   if (carry != nullptr && (y == nullptr || token_slot == nullptr || carry_stride < width)) return LS_E_SIZE;
   LS_COUNT(LS_K_GATED_SUM);
   if (y_dtype == LS_F32)
-    ls_launch(gated_sum_kernel<float>, dim3(tokens), dim3(256), 0, stream, residual, branches, n, z, bias, tokens, width,
-              (const float*)y, carry, (int64_t)carry_stride, token_slot);
+    gated_sum_launch<float>(residual, branches, n, z, bias, tokens, width, (const float*)y, carry, (int64_t)carry_stride,
+                            token_slot, stream);
   else if (y_dtype == LS_BF16)
-    ls_launch(gated_sum_kernel<__nv_bfloat16>, dim3(tokens), dim3(256), 0, stream, residual, branches, n, z, bias, tokens,
-              width, (const __nv_bfloat16*)y, carry, (int64_t)carry_stride, token_slot);
+    gated_sum_launch<__nv_bfloat16>(residual, branches, n, z, bias, tokens, width, (const __nv_bfloat16*)y, carry,
+                                    (int64_t)carry_stride, token_slot, stream);
   else return LS_E_DTYPE;
   return ls_launch_status();
 }

@@ -49,7 +49,7 @@ _SIGNATURES = {
                        c_float, c_int, c_int64, c_void_p, c_void_p],
         "ls_gated_sum": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p,
                          ctypes.c_longlong, c_void_p, c_void_p],
-        "ls_clamped_glu": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_float,
+        "ls_clamped_glu": [c_void_p, ctypes.c_longlong, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_float,
                            c_void_p, c_void_p, c_int, c_void_p],
         "ls_row_bias": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
         "ls_weighted_sum": [c_void_p, c_void_p, ctypes.c_longlong, c_int, ctypes.POINTER(c_float), c_void_p, c_int,
@@ -363,8 +363,8 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
 
 def clamped_glu(gate_up, bias, out, limit: float, alpha: float, residual=None, residual_bias=None) -> None:
     """out = g sigmoid(alpha g) (u + 1) with g = min(gate + b, limit), u = clamp(up + b, -limit, limit), from
-    ``gate_up`` [rows, 2 width] (gate columns, then up columns; float32 or the type of ``out``) and ``bias``
-    [2 width] or None.  With ``residual`` (float32 [rows, w]) and ``residual_bias`` [w] the same launch adds the
+    ``gate_up`` [rows, 2 width] (gate columns, then up columns; float32 or the type of ``out``; a view of some
+    columns of a wider tensor is fine) and ``bias`` [2 width] or None.  With ``residual`` (float32 [rows, w]) and ``residual_bias`` [w] the same launch adds the
     bias of the projection that follows into the residual stream."""
     rows, width = out.shape
     if gate_up.shape != (rows, 2 * width) or (bias is not None and bias.numel() != 2 * width):
@@ -375,8 +375,9 @@ def clamped_glu(gate_up, bias, out, limit: float, alpha: float, residual=None, r
     if bias is not None and residual_bias is not None and bias.dtype != residual_bias.dtype:
         raise KernelError("clamped_glu: biases of two element types")
     some = bias if bias is not None else residual_bias
+    gp, g_ld = _rows(gate_up, "gate_up")
     _check(library().ls_clamped_glu(
-        _dev(gate_up, "gate_up"), _code(gate_up), _opt(bias, "bias"), _code(some) if some is not None else F32,
+        gp, g_ld, _code(gate_up), _opt(bias, "bias"), _code(some) if some is not None else F32,
         _dev(out, "out"), _code(out), rows, width, float(limit), float(alpha), _opt(residual, "residual", torch.float32),
         _opt(residual_bias, "residual_bias"), residual.shape[1] if residual is not None else 0, _stream()), "clamped_glu")
 
@@ -869,13 +870,16 @@ def experts_tile_rows(tensor_cores: bool = False) -> int:
 def experts_route(logits, top: int, ids, weights, experts: int | None = None, softmax: bool = False,
                   correction=None) -> None:
     """The ``top`` experts of every token and their weights, from float32 ``logits`` [tokens, >= experts] (the
-    first ``experts`` columns; default all).  The weight is the sigmoid of the logit, or with ``softmax`` the
+    first ``experts`` columns; default all; a view of some columns of a wider tensor is fine).  The weight is the sigmoid of the logit, or with ``softmax`` the
     softmax over the experts; ``correction`` (float32 [experts]) is added to it for the choice alone."""
     tokens = logits.shape[0]
     experts = logits.shape[1] if experts is None else int(experts)
     if correction is not None and correction.numel() != experts:
         raise KernelError("experts_route: the correction does not match the experts")
-    _check(library("seq").ls_experts_route(_dev(logits, "logits", torch.float32), logits.shape[1], tokens, experts, top,
+    if logits.dtype != torch.float32:
+        raise KernelError("experts_route: logits must be float32")
+    lp, l_ld = _rows(logits, "logits")
+    _check(library("seq").ls_experts_route(lp, l_ld, tokens, experts, top,
                                            1 if softmax else 0, _opt(correction, "correction", torch.float32),
                                            _dev(ids, "ids", torch.int32), _dev(weights, "weights", torch.float32),
                                            _stream()), "experts_route")

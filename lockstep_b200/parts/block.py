@@ -103,6 +103,9 @@ _SHARED_NAMES = {"norm": "norm", "mixer": "mixer", "feed_forward": "mlp", "shift
                  "feed_forward_gate": "mlp_gate", "feed_forward_gate_bias": "mlp_gate.bias"}
 
 
+_SIDE_STREAMS: dict = {}
+
+
 class SharedNormBlock(Block):
     def __init__(self, layer_spec, runtime: Runtime):
         b = layer_spec.block
@@ -117,6 +120,7 @@ class SharedNormBlock(Block):
         if layer_spec.feed_forward.kind != "none":
             self.feed_forward = build_part("feed_forward", layer_spec.feed_forward, runtime)
         self.mix = self.w_gates = self.b_gates = None
+        self._side = None          # streams of the feed-forward and of the gates' product in steps of few tokens
 
     def _children(self):
         out = [(self.names["norm"], self.norm), (self.names["mixer"], self.mixer)]
@@ -180,18 +184,40 @@ class SharedNormBlock(Block):
         stores = self.mixer.can_overwrite and (self.feed_forward is None or self.feed_forward.can_overwrite)
         if not stores:
             K.row_bias(out.view(len(subs) * t, w), None)
-        if stores:
+        z = rt.rows(t, len(subs) * w, dtype=torch.float32) if self.gates else None
+        beside = stores and t <= K.FEW_TOKENS and rt.options.get("branch_streams", True) \
+            and (self.feed_forward is not None or self.gates)
+        if beside:
+            # a step of few tokens is a chain of launches of a handful of blocks each: the feed-forward and the
+            # gates' product run on streams of their own beside the mixer (in a recorded step: branches of the
+            # graph) and meet it again before the closing kernel
+            main = torch.cuda.current_stream()
+            if self._side is None:
+                # (the layers of a model share their two streams: a layer's branches have met again before the next layer)
+                self._side = _SIDE_STREAMS.setdefault(rt.device, [torch.cuda.Stream(device=rt.device) for _ in range(2)])
+            work = []
+            if self.feed_forward is not None:
+                work.append(lambda: self.feed_forward.forward(y, ctx, out[1], overwrite=True))
+            if self.gates:
+                work.append(lambda: K.gemm_nt(y, self.w_gates, z, err=rt.err))
+            for side, fn in zip(self._side, work):
+                side.wait_stream(main)                 # y and what came before it
+                with torch.cuda.stream(side):
+                    fn()
             self.mixer.forward(x, ctx, mixer_cache, out[0], overwrite=True)
-            if self.feed_forward is not None:
-                self.feed_forward.forward(y, ctx, out[1], overwrite=True)
+            for side, _ in zip(self._side, work):
+                main.wait_stream(side)
         else:
-            self.mixer.forward(x, ctx, mixer_cache, out[0])
-            if self.feed_forward is not None:
-                self.feed_forward.forward(y, ctx, out[1])
-        z = None
-        if self.gates:
-            z = rt.rows(t, len(subs) * w, dtype=torch.float32)
-            K.gemm_nt(y, self.w_gates, z, err=rt.err)
+            if stores:
+                self.mixer.forward(x, ctx, mixer_cache, out[0], overwrite=True)
+                if self.feed_forward is not None:
+                    self.feed_forward.forward(y, ctx, out[1], overwrite=True)
+            else:
+                self.mixer.forward(x, ctx, mixer_cache, out[0])
+                if self.feed_forward is not None:
+                    self.feed_forward.forward(y, ctx, out[1])
+            if self.gates:
+                K.gemm_nt(y, self.w_gates, z, err=rt.err)
         # the closing kernel: the (gated) sum into the residual stream, and the last row of every
         # request's portion into its slot for the next step's shift
         K.gated_sum(h, out, z, self.b_gates, carry=(y, carried, ctx.token_slot) if self.shift else None)

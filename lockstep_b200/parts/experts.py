@@ -12,8 +12,8 @@ one more expert of the same form that every token runs, added with the weight si
 where ``gate`` is set (else one).  The token's chosen experts are summed in order of rank, the
 shared expert last, and added into the residual stream.
 
-On the device: the router's product (the shared expert's gate rides on it as one more row), the
-choice, a sort of the step's (token, choice) pairs by expert (a counting sort made by one block),
+On the device: the router's product (the shared expert's gate rides on it as one more row, and the
+shared expert's first product as more rows behind it), the choice, a sort of the step's (token, choice) pairs by expert (a counting sort made by one block),
 the two products over the sorted rows tile by tile (a tile belongs to one expert), and the sum
 (csrc/experts.cu).  Nothing goes through the host, so the part can be recorded in a graph; the
 work lists are sized for the worst case, every expert holding a partly filled last tile.
@@ -82,13 +82,20 @@ class RoutedExperts(FeedForward):
         router = [t[n["router"]]]
         if self.shared and self.shared.get("gate"):
             router.append(t[n["shared_gate"]].reshape(1, self.h))        # its logit: one more column of the router's product
+        self.shared_at = 0
+        if self.shared:
+            # the shared expert's first product reads the same rows: it rides on the router's product too, from a
+            # column that is a multiple of 8 on (its activation then loads 16 bytes at a time)
+            rows = sum(r.shape[0] for r in router)
+            self.shared_at = -(-rows // 8) * 8
+            router.append(torch.zeros((self.shared_at - rows, self.h), dtype=router[0].dtype, device=router[0].device))
+            router.append(self._up(t, n["shared"]))
         self.w_router = torch.cat(router, dim=0).contiguous()
         self.bias = t[n["correction"]].to(torch.float32).contiguous() if self.correction else None
         names = [n["expert"].format(e) for e in range(self.E)]
         self.w_up = torch.stack([self._up(t, p) for p in names]).contiguous()                   # [E, f or 2 f, h]
         self.w_down = torch.stack([t[f"{p}.{n['down']}"] for p in names]).contiguous()          # [E, h, f]
         if self.shared:
-            self.w_shared_up = self._up(t, n["shared"]).contiguous()
             self.w_shared_down = t[f"{n['shared']}.{n['down']}"]
 
     def _activate(self, wide, rows, f):
@@ -96,11 +103,10 @@ class RoutedExperts(FeedForward):
         K.clamped_glu(wide, None, act, self.limit if self.limit > 0 else float("inf"), self.alpha)
         return act
 
-    def _shared(self, x, tokens):
-        """The shared expert on every token: float32 [tokens, hidden]."""
+    def _shared(self, first, tokens):
+        """The shared expert on every token, from its columns of the router's product: float32 [tokens, hidden]."""
         rt, f = self.rt, int(self.shared["ff"])
-        wide = rt.rows(tokens, 2 * f, dtype=torch.float32)
-        K.gemm_nt(x, self.w_shared_up, wide, err=rt.err)
+        wide = first[:, self.shared_at:self.shared_at + 2 * f]
         act = rt.rows(tokens, f)
         limit = float(self.shared.get("limit", self.limit))
         K.clamped_glu(wide, None, act, limit if limit > 0 else float("inf"), self.alpha)
@@ -157,7 +163,7 @@ class RoutedExperts(FeedForward):
         if plain:
             K.experts_combine(y, pair_row, residual, self.top)
             return
-        shared = self._shared(x, tokens) if self.shared else None
+        shared = self._shared(logits, tokens) if self.shared else None
         gate = logits[:, routed:routed + 1] if self.shared and self.shared.get("gate") else None
         K.experts_mix(y, pair_row, ids, None if on_input else weights, self.E, x, residual, shared=shared,
                       shared_gate=gate, store=overwrite)

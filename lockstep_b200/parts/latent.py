@@ -121,10 +121,12 @@ class LatentAttention(Mixer):
             x = x.materialize() if isinstance(x, NormedRows) else x
             raw = rt.rows(t, self.q_rank, dtype=torch.float32)
             K.gemm_nt(x, self.w_q_down, raw, err=rt.err)
-            cq = rt.rows(t, self.q_rank)
-            K.rmsnorm(raw, self.q_gain, cq, self.eps, rt.err)
             queries = rt.rows(t, H * (self.d + self.dr))
-            K.gemm_nt(cq, self.w_q_up, queries, err=rt.err)
+            # (few tokens: the second map's product norms its rows itself, with the bits of the separate kernel)
+            if not K.gemm_nt_tc_rmsnorm(raw, self.q_gain, self.eps, self.w_q_up, queries, K.EPILOGUE_STORE, rt.err):
+                cq = rt.rows(t, self.q_rank)
+                K.rmsnorm(raw, self.q_gain, cq, self.eps, rt.err)
+                K.gemm_nt(cq, self.w_q_up, queries, err=rt.err)
             kv = proj
         else:
             queries, kv = proj, None if self.borrows else proj[:, H * (self.d + self.dr):]

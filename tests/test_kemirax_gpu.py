@@ -327,6 +327,26 @@ def test_whole_models_in_every_cutting(zoo, model, plan_name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_sublayers_on_streams_of_their_own_give_the_bits_of_sublayers_in_turn(zoo, dtype):
+    """In steps of few tokens the feed-forward and the gates' product run on streams of their own beside the mixer
+    (recorded: branches of the graph).  The logits are those of a runner that takes them one after the other, bit
+    for bit, in decoding (recorded steps), in portions of a few tokens and in mixed batches."""
+    config, page = M.MODELS["S"]
+    folder, requests, want = zoo(config, dtype, LENGTHS["S"])
+    for plan_name in ("then_single", "portions", "mixed"):
+        steps = PLANS[plan_name](requests)
+        rows = {}
+        for streams in (True, False):
+            runner = make_runner(folder, dtype, page, steps)
+            runner.rt.options["branch_streams"] = streams
+            rows[streams] = H.run_plan(runner, steps)
+            if plan_name == "then_single" and runner.graphs is not None:
+                assert runner.graphs.replays > 100
+        for key, row in rows[True].items():
+            assert torch.equal(row, rows[False][key]), (plan_name, key)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_the_plain_model_reproduces_its_stream_layer_by_layer(zoo, dtype):
     """The residual stream after every layer run of the engine's own program against the plain
     model's: the first layer that differs is named."""
