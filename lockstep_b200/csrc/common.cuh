@@ -72,7 +72,7 @@ enum LsKernelId {
   LS_K_EXPERTS_ROUTE, LS_K_EXPERTS_PLAN, LS_K_EXPERTS_UP, LS_K_EXPERTS_DOWN, LS_K_EXPERTS_COMBINE,
   LS_K_EXPERTS_GATHER, LS_K_EXPERTS_UP_TC, LS_K_EXPERTS_DOWN_TC, LS_K_TANH, LS_K_DOUBLE_EXP_DECAY,
   LS_K_CLAMPED_GLU, LS_K_ROW_BIAS, LS_K_WEIGHTED_SUM, LS_K_GLA_RULE, LS_K_SIGMOID_POWER_DECAY, LS_K_LATENT_FINISH,
-  LS_K_HEADS_PRODUCT, LS_K_GATED_SUM, LS_K_EXPERTS_MIX,
+  LS_K_HEADS_PRODUCT, LS_K_GATED_SUM, LS_K_EXPERTS_MIX, LS_K_RMSNORM_SHIFT,
   LS_K_COUNT
 };
 #define LS_KERNEL_NAMES                                                                                  \
@@ -83,7 +83,7 @@ enum LsKernelId {
   "wkv_rule,head_rms_gate,experts_route,experts_plan,experts_up,experts_down,experts_combine,"     \
   "experts_gather,experts_up_tc,experts_down_tc,tanh_rows,double_exp_decay,"                      \
   "clamped_glu,row_bias,weighted_sum,gla_rule,sigmoid_power_decay,latent_finish,heads_product,"  \
-  "gated_sum,experts_mix"
+  "gated_sum,experts_mix,rmsnorm_shift"
 // one table per library: hidden, so that two libraries loaded into one process do not share it
 __attribute__((visibility("hidden"))) inline unsigned long long ls_kernel_launches[LS_K_COUNT];
 #define LS_COUNT(id) (++ls_kernel_launches[id])

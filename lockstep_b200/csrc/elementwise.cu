@@ -656,5 +656,98 @@ LS_API int ls_gated_sum(float* residual, const float* branches, int n, const flo
   return ls_launch_status();
 }
 
+// --------------------------------------------------------------------------
+// RMSNorm and token shift in one pass over the rows:
+//   y[t] = h[t] * rsqrt(mean(h[t]^2) + eps) * gain,   x[t] = y[t] + (before - y[t]) * mu
+// with `before` = y[t - 1] where token t - 1 belongs to the same slot (its norm is made again here, with the
+// same sums), else the row carried in carry[slot[t]] from the step before (zeros for a new request).  A
+// warp per row; the sums, products and roundings are those of rmsnorm_kernel followed by the shift of the
+// rounded rows, so the bits are the same.
+// --------------------------------------------------------------------------
+template <typename TO, typename TG>
+__global__ void __launch_bounds__(128)
+rmsnorm_shift_kernel(const float* __restrict__ h, const TG* __restrict__ gain, const float* __restrict__ mu,
+                     const float* __restrict__ carry, int64_t carry_stride, const int* __restrict__ token_slot,
+                     TO* __restrict__ y, TO* __restrict__ x, int tokens, int width, float eps) {
+  ls_dependency_sync();
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (t >= tokens) return;
+  const int slot = token_slot[t];
+  const bool inside = t > 0 && token_slot[t - 1] == slot;
+  const float* cur = h + (int64_t)t * width;
+  const float* prev = h + (int64_t)(inside ? t - 1 : t) * width;
+  const float* kept = carry + (int64_t)slot * carry_stride;
+  const bool vec = (width & 3) == 0 && ((uintptr_t)h & 15) == 0;
+  const bool vec_out = vec && ((uintptr_t)y & (4 * sizeof(TO) - 1)) == 0 && ((uintptr_t)x & (4 * sizeof(TO) - 1)) == 0 &&
+                       ((uintptr_t)gain & (4 * sizeof(TG) - 1)) == 0 && ((uintptr_t)mu & 15) == 0 &&
+                       ((uintptr_t)kept & 15) == 0 && (carry_stride & 3) == 0;
+  auto sum_squares = [&](const float* r) {
+    float ss = 0.f;
+    if (vec) {
+      for (int g = lane; g < (width >> 2); g += 32) {
+        const float4 v = *reinterpret_cast<const float4*>(r + 4 * g);
+        ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+      }
+    } else {
+      for (int i = lane; i < width; i += 32) ss = fmaf(r[i], r[i], ss);
+    }
+    return ls_warp_sum(ss);
+  };
+  const float rstd = 1.0f / sqrtf(sum_squares(cur) / (float)width + eps);
+  const float rstd_prev = inside ? 1.0f / sqrtf(sum_squares(prev) / (float)width + eps) : 0.f;
+  auto rounded = [](float v) { return ls_to_float<TO>(ls_from_float<TO>(v)); };
+  if (vec_out) {
+    for (int g = lane; g < (width >> 2); g += 32) {
+      const int c = 4 * g;
+      const float4 v = *reinterpret_cast<const float4*>(cur + c);
+      const float4 gn = ls_load4<TG>(gain + c);
+      const float4 m = *reinterpret_cast<const float4*>(mu + c);
+      const float own[4] = {rounded(v.x * rstd * gn.x), rounded(v.y * rstd * gn.y), rounded(v.z * rstd * gn.z),
+                            rounded(v.w * rstd * gn.w)};
+      float before[4];
+      if (inside) {
+        const float4 p = *reinterpret_cast<const float4*>(prev + c);
+        before[0] = rounded(p.x * rstd_prev * gn.x); before[1] = rounded(p.y * rstd_prev * gn.y);
+        before[2] = rounded(p.z * rstd_prev * gn.z); before[3] = rounded(p.w * rstd_prev * gn.w);
+      } else {
+        const float4 p = *reinterpret_cast<const float4*>(kept + c);
+        before[0] = p.x; before[1] = p.y; before[2] = p.z; before[3] = p.w;
+      }
+      ls_store4<TO>(y + (int64_t)t * width + c, own[0], own[1], own[2], own[3]);
+      ls_store4<TO>(x + (int64_t)t * width + c, fmaf(before[0] - own[0], m.x, own[0]), fmaf(before[1] - own[1], m.y, own[1]),
+                    fmaf(before[2] - own[2], m.z, own[2]), fmaf(before[3] - own[3], m.w, own[3]));
+    }
+  } else {
+    for (int c = lane; c < width; c += 32) {
+      const float gn = ls_to_float<TG>(gain[c]);
+      const float own = rounded(cur[c] * rstd * gn);
+      const float before = inside ? rounded(prev[c] * rstd_prev * gn) : kept[c];
+      y[(int64_t)t * width + c] = ls_from_float<TO>(own);
+      x[(int64_t)t * width + c] = ls_from_float<TO>(fmaf(before - own, mu[c], own));
+    }
+  }
+}
+
+LS_API int ls_rmsnorm_shift(const float* h, const void* gain, int gain_dtype, const float* mu, const float* carry,
+                            long long carry_stride, const int* token_slot, void* y, void* x, int out_dtype, int tokens,
+                            int width, float eps, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (width <= 0 || carry_stride < width) return LS_E_SIZE;
+  const int warps = tokens >= 1024 ? 4 : 1;
+  const int blocks = (tokens + warps - 1) / warps;
+  LS_COUNT(LS_K_RMSNORM_SHIFT);
+#define LS_RMS_SHIFT(TO, TG)                                                                                          \
+  ls_launch(rmsnorm_shift_kernel<TO, TG>, blocks, warps * 32, 0, stream, h, (const TG*)gain, mu, carry,               \
+            (int64_t)carry_stride, token_slot, (TO*)y, (TO*)x, tokens, width, eps)
+  if (out_dtype == LS_F32 && gain_dtype == LS_F32) LS_RMS_SHIFT(float, float);
+  else if (out_dtype == LS_F32 && gain_dtype == LS_BF16) LS_RMS_SHIFT(float, __nv_bfloat16);
+  else if (out_dtype == LS_BF16 && gain_dtype == LS_F32) LS_RMS_SHIFT(__nv_bfloat16, float);
+  else if (out_dtype == LS_BF16 && gain_dtype == LS_BF16) LS_RMS_SHIFT(__nv_bfloat16, __nv_bfloat16);
+  else return LS_E_DTYPE;
+#undef LS_RMS_SHIFT
+  return ls_launch_status();
+}
+
 // Switches programmatic dependent launch of this library's kernels on or off.
 LS_API void ls_set_dependent_launch_core(int on) { ls_dependent_launch = on ? 1 : 0; }

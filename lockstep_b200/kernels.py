@@ -47,6 +47,8 @@ _SIGNATURES = {
         "ls_embed_gather": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
         "ls_rmsnorm": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
                        c_float, c_int, c_int64, c_void_p, c_void_p],
+        "ls_rmsnorm_shift": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_void_p, c_void_p,
+                             c_int, c_int, c_int, c_float, c_void_p],
         "ls_gated_sum": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p,
                          ctypes.c_longlong, c_void_p, c_void_p],
         "ls_clamped_glu": [c_void_p, ctypes.c_longlong, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_float,
@@ -294,6 +296,21 @@ def rmsnorm(x: torch.Tensor, gain: torch.Tensor, out: torch.Tensor, eps: float, 
         _dev(x, "x", torch.float32), _opt(row_index, "row_index", torch.int32), _dev(gain, "gain"),
         _code(gain), _dev(out, "out"), _code(out), rows, width, x.shape[0], float(eps), int(groups), x.shape[1],
         _dev(err, "err", torch.int32), _stream()), "rmsnorm")
+
+
+def rmsnorm_shift(h, gain, eps: float, mu, state, token_slot, y, x) -> None:
+    """y = rmsnorm(h) (``gain`` per column) and x[t] = y[t] + (y[t - 1] - y[t]) * mu in one pass, the row before a
+    portion's first one taken from ``state[slot]`` (float32 [slots, >= width]); bit for bit what ``rmsnorm``
+    followed by ``shift_mix`` gives.  ``h`` float32 [tokens, width]; ``y`` and ``x`` of one element type."""
+    tokens, width = h.shape
+    if y.shape != h.shape or x.shape != h.shape or y.dtype != x.dtype or gain.numel() != width or mu.numel() != width:
+        raise KernelError("rmsnorm_shift: shapes do not agree")
+    if state.dim() != 2 or state.shape[1] < width or token_slot.numel() != tokens:
+        raise KernelError("rmsnorm_shift: the carried rows do not match")
+    _check(library().ls_rmsnorm_shift(
+        _dev(h, "h", torch.float32), _dev(gain, "gain"), _code(gain), _dev(mu, "mu", torch.float32),
+        _dev(state, "state", torch.float32), state.stride(0), _dev(token_slot, "token_slot", torch.int32),
+        _dev(y, "y"), _dev(x, "x"), _code(y), tokens, width, float(eps), _stream()), "rmsnorm_shift")
 
 
 def gated_sum(residual, branches, z, bias, carry=None) -> None:

@@ -109,6 +109,19 @@ class Runtime:
         return torch.empty((-(-rows // step) * step, *tail), dtype=dtype, device=self.device)[:rows]
 
 
+_SIDE_STREAMS: dict = {}
+
+
+def side_stream(device: torch.device, index: int) -> "torch.cuda.Stream":
+    """Stream ``index`` of the few streams on which, in steps of few tokens, a part runs a branch of its work
+    beside the rest (in a recorded step: a branch of the graph).  The parts of a model share them: a branch
+    has met the stream it left before that stream goes on.  A part uses an index that no part around it uses."""
+    key = (str(device), int(index))
+    if key not in _SIDE_STREAMS:
+        _SIDE_STREAMS[key] = torch.cuda.Stream(device=device)
+    return _SIDE_STREAMS[key]
+
+
 class Part:
     """Base of all parts."""
 

@@ -19,7 +19,8 @@ import torch
 
 from .. import kernels as K
 from ..config.spec import own_tensors, tensor_name
-from .base import Block, CacheNeed, Runtime, WeightSpec, build_part, register_part
+from .base import Block, CacheNeed, Runtime, WeightSpec, build_part, register_part, side_stream
+from .norm import RMSNorm
 
 _DEFAULT_NAMES = {
     "mixer_norm": "input_layernorm",
@@ -103,9 +104,6 @@ _SHARED_NAMES = {"norm": "norm", "mixer": "mixer", "feed_forward": "mlp", "shift
                  "feed_forward_gate": "mlp_gate", "feed_forward_gate_bias": "mlp_gate.bias"}
 
 
-_SIDE_STREAMS: dict = {}
-
-
 class SharedNormBlock(Block):
     def __init__(self, layer_spec, runtime: Runtime):
         b = layer_spec.block
@@ -173,12 +171,16 @@ class SharedNormBlock(Block):
 
     def forward(self, h, ctx, cache):
         rt, t, w = self.rt, h.shape[0], self.width
-        y = self.norm.forward(h)
         mixer_cache, carried = (cache.parts[0], cache.parts[1].state) if self.shift else (cache, None)
-        x = y
-        if self.shift:
-            x = rt.rows(t, w)
-            K.shift_mix(y, self.mix, carried, 0, ctx.token_slot, x.view(1, t, w))
+        if self.shift and isinstance(self.norm, RMSNorm) and self.norm.groups == 1:
+            # the norm and the shift in one pass over the rows (the bits of the two kernels in turn)
+            y, x = rt.rows(t, w), rt.rows(t, w)
+            K.rmsnorm_shift(h, self.norm.gain, self.norm.eps, self.mix, carried, ctx.token_slot, y, x)
+        else:
+            x = y = self.norm.forward(h)
+            if self.shift:
+                x = rt.rows(t, w)
+                K.shift_mix(y, self.mix, carried, 0, ctx.token_slot, x.view(1, t, w))
         subs = self._sublayers()
         out = rt.rows(len(subs) * t, w, dtype=torch.float32).view(len(subs), t, w)
         stores = self.mixer.can_overwrite and (self.feed_forward is None or self.feed_forward.can_overwrite)
@@ -193,8 +195,7 @@ class SharedNormBlock(Block):
             # graph) and meet it again before the closing kernel
             main = torch.cuda.current_stream()
             if self._side is None:
-                # (the layers of a model share their two streams: a layer's branches have met again before the next layer)
-                self._side = _SIDE_STREAMS.setdefault(rt.device, [torch.cuda.Stream(device=rt.device) for _ in range(2)])
+                self._side = [side_stream(rt.device, 0), side_stream(rt.device, 1)]
             work = []
             if self.feed_forward is not None:
                 work.append(lambda: self.feed_forward.forward(y, ctx, out[1], overwrite=True))

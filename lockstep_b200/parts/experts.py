@@ -24,7 +24,7 @@ from __future__ import annotations
 import torch
 
 from .. import kernels as K
-from .base import FeedForward, Runtime, WeightSpec, register_part
+from .base import FeedForward, Runtime, WeightSpec, register_part, side_stream
 
 _DEFAULT_NAMES = {"router": "router", "correction": "correction", "expert": "e{}", "up": "up", "gate": "gate",
                   "down": "down", "shared": "shared", "shared_gate": "shared.sg"}
@@ -121,6 +121,14 @@ class RoutedExperts(FeedForward):
         routed = self.E + self.identity
         logits = rt.rows(tokens, self.w_router.shape[0], dtype=f32)
         K.gemm_nt(x, self.w_router, logits, err=rt.err)
+        # few tokens: the shared expert runs on a stream of its own beside the routed ones (every kernel here is a
+        # handful of blocks) and meets them before the sum
+        shared, shared_on = None, None
+        if self.shared and tokens <= K.FEW_TOKENS and rt.options.get("branch_streams", True) and x.is_cuda:
+            shared_on = side_stream(rt.device, 2)
+            shared_on.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(shared_on):
+                shared = self._shared(logits, tokens)
         ids = rt.rows(tokens, self.top, dtype=i32)
         weights = rt.rows(tokens, self.top, dtype=f32)
         K.experts_route(logits, self.top, ids, weights, experts=routed, softmax=self.score == "softmax",
@@ -163,7 +171,10 @@ class RoutedExperts(FeedForward):
         if plain:
             K.experts_combine(y, pair_row, residual, self.top)
             return
-        shared = self._shared(logits, tokens) if self.shared else None
+        if shared_on is not None:
+            torch.cuda.current_stream().wait_stream(shared_on)
+        elif self.shared:
+            shared = self._shared(logits, tokens)
         gate = logits[:, routed:routed + 1] if self.shared and self.shared.get("gate") else None
         K.experts_mix(y, pair_row, ids, None if on_input else weights, self.E, x, residual, shared=shared,
                       shared_gate=gate, store=overwrite)

@@ -132,6 +132,35 @@ def test_token_shift_carries_a_row_and_the_gated_sum_keeps_it(dtype, width):
     assert float((want[2] - rows[2].double()).abs().max()) > 0.1
 
 
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("width", [40, 52, 7, 1024])
+def test_norm_and_shift_in_one_pass_give_the_bits_of_the_two_in_turn(dtype, width):
+    from lockstep_b200 import kernels as K
+
+    g = torch.Generator().manual_seed(width)
+    slots = [2] * 5 + [0] * 1 + [1] * 3 + [3] * 1100          # (more than a thousand rows: four rows a block)
+    tokens = len(slots)
+    h = (torch.randn(tokens, width, generator=g) * torch.linspace(0.05, 9.0, tokens)[:, None]).to(DEV)
+    gain = torch.full((width,), 1.3).to(dtype).to(DEV)
+    mu = torch.rand(1, width, generator=g).to(DEV)
+    state = torch.randn(5, width + 4, generator=g).to(DEV)
+    slot = torch.tensor(slots, dtype=torch.int32, device=DEV)
+    err = K.new_error_word(DEV)
+    y0 = torch.empty(tokens, width, dtype=dtype, device=DEV)
+    K.rmsnorm(h, gain, y0, 1e-4, err)
+    x0 = torch.empty(1, tokens, width, dtype=dtype, device=DEV)
+    K.shift_mix(y0, mu, state, 0, slot, x0)
+    y1, x1 = torch.empty_like(y0), torch.empty_like(y0)
+    K.rmsnorm_shift(h, gain, 1e-4, mu, state, slot, y1, x1)
+    K.raise_on_fault(err)
+    assert torch.equal(y0, y1) and torch.equal(x0[0], x1)
+    want = plain.scalar_rms_norm(h.double().cpu(), torch.tensor(1.3).to(dtype).double(), 1e-4)
+    assert float((y1.double().cpu() - want).abs().max()) < (5e-6 if dtype == F32 else 3e-2)
+    # every portion's first row leans on its slot's carried row, the others on the row before
+    first = plain.shifted(want[:5], mu.double().cpu()[0], before=state[2, :width].double().cpu())
+    assert float((x1[:5].double().cpu() - first).abs().max()) < (1e-5 if dtype == F32 else 6e-2)
+
+
 @pytest.mark.parametrize("experts, top", [(12, 3), (5, 5), (40, 4), (1, 1), (300, 7)])
 def test_softmax_routing_chooses_by_corrected_scores_and_weighs_by_plain_ones(experts, top):
     from lockstep_b200 import kernels as K
