@@ -24,13 +24,11 @@ constexpr int TILE_M = 64, TILE_N = 64, TILE_K = 16;
 // softmax 0: weight = sigmoid(logit); 1: weight = softmax over the `experts` logits (the largest taken off, the
 // exponentials summed lane by lane over ascending experts, then by an xor tree: an order the token alone fixes).
 // correction (or null) [experts]: added to the weight for the choice only.
-__global__ void __launch_bounds__(ROUTE_WARPS * 32) route_kernel(const float* __restrict__ logits, int64_t ld, int tokens,
-                                                                 int experts, int top, int softmax,
-                                                                 const float* __restrict__ correction,
-                                                                 int* __restrict__ ids, float* __restrict__ weights) {
-  ls_dependency_sync();
-  const int lane = threadIdx.x & 31, t = blockIdx.x * ROUTE_WARPS + (threadIdx.x >> 5);
-  if (t >= tokens) return;
+// (one warp: token t)
+__device__ __forceinline__ void route_token(const float* __restrict__ logits, int64_t ld, int t, int experts, int top,
+                                            int softmax, const float* __restrict__ correction, int* __restrict__ ids,
+                                            float* __restrict__ weights) {
+  const int lane = threadIdx.x & 31;
   float z[MAX_PER_LANE];     // the expert's score
   float pick[MAX_PER_LANE];  // what the choice compares
 #pragma unroll
@@ -92,22 +90,31 @@ __global__ void __launch_bounds__(ROUTE_WARPS * 32) route_kernel(const float* __
   }
 }
 
+__global__ void __launch_bounds__(ROUTE_WARPS * 32) route_kernel(const float* __restrict__ logits, int64_t ld, int tokens,
+                                                                 int experts, int top, int softmax,
+                                                                 const float* __restrict__ correction,
+                                                                 int* __restrict__ ids, float* __restrict__ weights) {
+  ls_dependency_sync();
+  const int t = blockIdx.x * ROUTE_WARPS + (threadIdx.x >> 5);
+  if (t >= tokens) return;
+  route_token(logits, ld, t, experts, top, softmax, correction, ids, weights);
+}
+
 // plan [0] = tiles, then (expert, first row, rows) per tile; row_token / row_weight per sorted
-// row; pair_row [T * top]: the sorted row of a pair
-__global__ void __launch_bounds__(PLAN_THREADS) plan_kernel(const int* __restrict__ ids, const float* __restrict__ weights,
-                                                            int pairs, int top, int experts, int tile_rows,
-                                                            int* __restrict__ plan, int max_tiles,
-                                                            int* __restrict__ row_token,
-                                                            float* __restrict__ row_weight, int* __restrict__ pair_row,
-                                                            int* err) {
+// row; pair_row [T * top]: the sorted row of a pair.  The work of one block of any size.
+// (ids and weights are not marked restrict: the kernel that also makes them writes them before this reads them)
+__device__ __forceinline__ void plan_block(const int* ids, const float* weights, int pairs,
+                                           int top, int experts, int tile_rows, int* __restrict__ plan, int max_tiles,
+                                           int* __restrict__ row_token, float* __restrict__ row_weight,
+                                           int* __restrict__ pair_row, int* err) {
   // (ids outside 0 .. experts - 1 get no row: the caller's identity experts)
   extern __shared__ int sm[];
   int* count = sm;                  // [experts]
   int* first = count + experts;     // [experts]
   int* cursor = first + experts;    // [experts]
   __shared__ int sorted_rows;
-  ls_dependency_sync();
   const int tid = threadIdx.x;
+  const int PLAN_THREADS = blockDim.x;
   for (int e = tid; e < experts; e += PLAN_THREADS) count[e] = cursor[e] = 0;
   __syncthreads();
   for (int p = tid; p < pairs; p += PLAN_THREADS) {
@@ -152,6 +159,30 @@ __global__ void __launch_bounds__(PLAN_THREADS) plan_kernel(const int* __restric
     row_token[row] = 0;
     row_weight[row] = 0.f;
   }
+}
+
+__global__ void __launch_bounds__(PLAN_THREADS) plan_kernel(const int* __restrict__ ids, const float* __restrict__ weights,
+                                                            int pairs, int top, int experts, int tile_rows,
+                                                            int* __restrict__ plan, int max_tiles,
+                                                            int* __restrict__ row_token,
+                                                            float* __restrict__ row_weight, int* __restrict__ pair_row,
+                                                            int* err) {
+  ls_dependency_sync();
+  plan_block(ids, weights, pairs, top, experts, tile_rows, plan, max_tiles, row_token, row_weight, pair_row, err);
+}
+
+// The choice and the plan of a step of few tokens in one block: its warps take the tokens in turn, then the
+// block sorts the pairs.  `real`: the experts that have rows (the first of the `experts` the router scores).
+__global__ void __launch_bounds__(ROUTE_WARPS * 32) route_plan_kernel(
+    const float* __restrict__ logits, int64_t ld, int tokens, int experts, int top, int softmax,
+    const float* __restrict__ correction, int* ids, float* weights, int real, int tile_rows,
+    int* __restrict__ plan, int max_tiles, int* __restrict__ row_token, float* __restrict__ row_weight,
+    int* __restrict__ pair_row, int* err) {
+  ls_dependency_sync();
+  for (int t = threadIdx.x >> 5; t < tokens; t += ROUTE_WARPS)
+    route_token(logits, ld, t, experts, top, softmax, correction, ids, weights);
+  __syncthreads();                  // (the block's own writes to ids and weights are visible to it behind the barrier)
+  plan_block(ids, weights, tokens * top, top, real, tile_rows, plan, max_tiles, row_token, row_weight, pair_row, err);
 }
 
 // One tile of an expert's product on the CUDA cores: C[rows, N] = A[rows, K] . W_e[N, K]^T.
@@ -288,6 +319,23 @@ LS_API int ls_experts_route(const float* logits, long long ld, int tokens, int e
   LS_COUNT(LS_K_EXPERTS_ROUTE);
   cudaError_t e = ls_launch(route_kernel, dim3((tokens + ROUTE_WARPS - 1) / ROUTE_WARPS), dim3(ROUTE_WARPS * 32), 0, stream,
                             logits, (int64_t)ld, tokens, experts, top, softmax, correction, ids, weights);
+  if (e != cudaSuccess) return (int)e;
+  return ls_launch_status();
+}
+
+// Both in one launch of one block, for steps of few tokens (the same choices, weights and plan).
+LS_API int ls_experts_route_plan(const float* logits, long long ld, int tokens, int experts, int top, int softmax,
+                                 const float* correction, int* ids, float* weights, int real, int tile_rows, int* plan,
+                                 int max_tiles, int* row_token, float* row_weight, int* pair_row, int* err,
+                                 cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (experts <= 0 || experts > 32 * MAX_PER_LANE || top <= 0 || top > experts || ld < experts) return LS_E_SIZE;
+  if (real <= 0 || real > experts || max_tiles <= 0 || tile_rows <= 0) return LS_E_SIZE;
+  LS_COUNT(LS_K_EXPERTS_ROUTE);
+  LS_COUNT(LS_K_EXPERTS_PLAN);
+  cudaError_t e = ls_launch(route_plan_kernel, dim3(1), dim3(ROUTE_WARPS * 32), sizeof(int) * 3 * (size_t)real, stream,
+                            logits, (int64_t)ld, tokens, experts, top, softmax, correction, ids, weights, real, tile_rows,
+                            plan, max_tiles, row_token, row_weight, pair_row, err);
   if (e != cudaSuccess) return (int)e;
   return ls_launch_status();
 }

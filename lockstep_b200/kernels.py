@@ -124,6 +124,8 @@ _SIGNATURES["seq"] = {
                        ctypes.c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "ls_experts_plan": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                         c_void_p, c_void_p],
+    "ls_experts_route_plan": [c_void_p, ctypes.c_longlong, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                              c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     "ls_experts_tc_tile_rows": [],
     "ls_experts_gather": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
     "ls_experts_product_tc": [c_int, c_void_p, c_int, c_void_p, ctypes.c_longlong, c_void_p, c_int, c_void_p, c_void_p,
@@ -931,6 +933,22 @@ def experts_plan(ids, weights, experts: int, tile_rows: int, plan, max_tiles: in
         _dev(plan, "plan", torch.int32), max_tiles, _dev(row_token, "row_token", torch.int32),
         _dev(row_weight, "row_weight", torch.float32), _dev(pair_row, "pair_row", torch.int32),
         _dev(err, "err", torch.int32), _stream()), "experts_plan")
+
+
+def experts_route_plan(logits, top: int, ids, weights, experts: int, softmax: bool, correction, real: int, tile_rows: int,
+                       plan, max_tiles: int, row_token, row_weight, pair_row, err) -> None:
+    """``experts_route`` and ``experts_plan`` (over the first ``real`` experts) in one launch of one block, for steps
+    of few tokens: the same choices, weights and plan."""
+    tokens = logits.shape[0]
+    if logits.dtype != torch.float32 or (correction is not None and correction.numel() != experts):
+        raise KernelError("experts_route_plan: the logits or the correction do not match")
+    lp, l_ld = _rows(logits, "logits")
+    _check(library("seq").ls_experts_route_plan(
+        lp, l_ld, tokens, experts, top, 1 if softmax else 0, _opt(correction, "correction", torch.float32),
+        _dev(ids, "ids", torch.int32), _dev(weights, "weights", torch.float32), real, tile_rows,
+        _dev(plan, "plan", torch.int32), max_tiles, _dev(row_token, "row_token", torch.int32),
+        _dev(row_weight, "row_weight", torch.float32), _dev(pair_row, "pair_row", torch.int32),
+        _dev(err, "err", torch.int32), _stream()), "experts_route_plan")
 
 
 def experts_product(mode: int, plan, max_tiles: int, a, row_token, row_weight, w, c) -> None:

@@ -131,8 +131,6 @@ class RoutedExperts(FeedForward):
                 shared = self._shared(logits, tokens)
         ids = rt.rows(tokens, self.top, dtype=i32)
         weights = rt.rows(tokens, self.top, dtype=f32)
-        K.experts_route(logits, self.top, ids, weights, experts=routed, softmax=self.score == "softmax",
-                        correction=self.bias)
         # bfloat16 products go to the tensor cores where TMA can address the rows (16-byte pitches)
         tensor_cores = (rt.dtype == torch.bfloat16 and K.USE_TENSOR_CORES[0] and self.h % 8 == 0 and self.f % 8 == 0)
         tile = K.experts_tile_rows(tensor_cores)
@@ -141,7 +139,14 @@ class RoutedExperts(FeedForward):
         row_token = rt.rows(pairs, dtype=i32)
         row_weight = rt.rows(pairs, dtype=f32)
         pair_row = rt.rows(pairs, dtype=i32)
-        K.experts_plan(ids, weights, self.E, tile, plan, max_tiles, row_token, row_weight, pair_row, rt.err)
+        if tokens <= K.FEW_TOKENS:
+            # few tokens: the choice and the plan in one launch of one block
+            K.experts_route_plan(logits, self.top, ids, weights, routed, self.score == "softmax", self.bias, self.E, tile,
+                                 plan, max_tiles, row_token, row_weight, pair_row, rt.err)
+        else:
+            K.experts_route(logits, self.top, ids, weights, experts=routed, softmax=self.score == "softmax",
+                            correction=self.bias)
+            K.experts_plan(ids, weights, self.E, tile, plan, max_tiles, row_token, row_weight, pair_row, rt.err)
         on_input = self.scale == "input"
         # one expert a token and nothing beside it: the second product adds into the residual stream itself (an
         # element has one writer); else its rows go through memory and are added in order of rank

@@ -190,6 +190,43 @@ def test_softmax_routing_chooses_by_corrected_scores_and_weighs_by_plain_ones(ex
         assert float(want_w.sum(-1).max()) < 0.999
 
 
+@pytest.mark.parametrize("tokens, real, identity, top", [(1, 5, 2, 3), (8, 32, 4, 4), (32, 40, 0, 7), (19, 1, 6, 2)])
+def test_choice_and_plan_in_one_launch_are_those_of_the_two_in_turn(tokens, real, identity, top):
+    from lockstep_b200 import kernels as K
+
+    g = torch.Generator().manual_seed(tokens)
+    experts, pairs, tile = real + identity, tokens * top, 64
+    logits = (torch.randn(tokens, experts + 3, generator=g) * 2).to(DEV)
+    correction = (torch.randn(experts, generator=g) * 0.2).to(DEV)
+    max_tiles = min(pairs, pairs // tile + real)
+    err = K.new_error_word(DEV)
+
+    def buffers():
+        i32, f32 = torch.int32, torch.float32
+        return dict(ids=torch.full((tokens, top), -7, dtype=i32, device=DEV), weights=torch.zeros(tokens, top, device=DEV),
+                    plan=torch.full((1 + 3 * max_tiles,), -7, dtype=i32, device=DEV),
+                    row_token=torch.full((pairs,), -7, dtype=i32, device=DEV), row_weight=torch.full((pairs,), -7.0, device=DEV),
+                    pair_row=torch.full((pairs,), -7, dtype=i32, device=DEV))
+
+    a, b = buffers(), buffers()
+    K.experts_route(logits, top, a["ids"], a["weights"], experts=experts, softmax=True, correction=correction)
+    K.experts_plan(a["ids"], a["weights"], real, tile, a["plan"], max_tiles, a["row_token"], a["row_weight"], a["pair_row"], err)
+    K.experts_route_plan(logits, top, b["ids"], b["weights"], experts, True, correction, real, tile, b["plan"], max_tiles,
+                         b["row_token"], b["row_weight"], b["pair_row"], err)
+    K.raise_on_fault(err)
+    assert torch.equal(a["ids"], b["ids"]) and torch.equal(a["weights"], b["weights"])
+    tiles = int(a["plan"][0])
+    assert tiles == int(b["plan"][0]) and torch.equal(a["plan"][:1 + 3 * tiles], b["plan"][:1 + 3 * tiles])
+    # rows of one expert may come in either order (they are handed out by atomic counters): the sets agree
+    real_pair = (a["ids"].flatten() < real).cpu()
+    assert torch.equal(a["pair_row"].cpu()[real_pair].sort().values, b["pair_row"].cpu()[real_pair].sort().values)
+    for name in ("a", "b"):
+        d = a if name == "a" else b
+        rows = d["pair_row"].cpu()[real_pair].long()
+        assert torch.equal(d["row_token"].cpu()[rows].long(), (torch.arange(pairs) // top)[real_pair])
+        assert torch.equal(d["row_weight"].cpu()[rows], d["weights"].flatten().cpu()[real_pair])
+
+
 @pytest.mark.parametrize("dtype", [F32, BF16])
 @pytest.mark.parametrize("store", [False, True])
 def test_mixing_real_identity_and_shared_experts(dtype, store):
