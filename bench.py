@@ -574,7 +574,7 @@ def kernel_times(runner, entries_of, steps=3):
              "attention_prefill_tc", "attention_combine", "qkv_finish", "find_portions", "delta_prep", "shift_mix",
              "tanh_rows", "double_exp_decay", "state_rule", "head_rms_gate", "experts_route", "experts_plan", "experts_product",
              "experts_product_tc", "experts_gather", "experts_combine", "latent_finish", "heads_product",
-             "sigmoid_power_decay", "clamped_glu", "row_bias", "weighted_sum", "gated_sum", "experts_mix", "rmsnorm_shift"]
+             "sigmoid_power_decay", "clamped_glu", "row_bias", "weighted_sum", "gated_sum", "experts_mix", "rmsnorm_shift", "experts_route_plan"]
     records, saved, graphs, turn = [], {}, runner.graphs, [0]
     runner.graphs = None
 
