@@ -89,6 +89,42 @@ def layers_model(layers, width=48, vocab=97, eps=1e-5):
     return model(width, vocab, eps, list(layers))
 
 
+def random_config(seed: int) -> dict:
+    """A configuration drawn from a seed: widths of 192 to 512, six to twelve layers in any order of the two
+    mixers, readers of any earlier lender, cached rows of 80 to 256 elements, experts with and without identity and
+    shared experts, layers without a feed-forward."""
+    import random
+
+    r = random.Random(seed)
+    width, vocab = r.choice([256, 320, 384, 448, 512, 192]), r.choice([384, 500, 512, 640, 1000])
+    rot_dim = r.choice([16, 32, 64])
+    kv_rank = r.choice([64, 96, 128, 160, 192 - (rot_dim if rot_dim == 64 else 0)])
+    scaling = None
+    if r.random() < 0.8:
+        scaling = (r.choice([2.0, 4.0, 8.0, 16.0]), r.choice([256, 512, 1024, 2048]), r.choice([32.0, 16.0, 8.0]),
+                   r.choice([1.0, 2.0, 0.5]))
+    base = r.choice([10000.0, 500000.0, 1000.0])
+    layers, lenders = [], []
+    for i in range(r.choice([6, 8, 10, 12])):
+        if r.random() < 0.3:
+            layer = gla(r.choice([2, 4, 6]), r.choice([32, 48, 64, 128]), r.choice([32, 64, 96]), tau=r.choice([4.0, 16.0, 8.0]),
+                        decay_rank=r.choice([8, 16, 24]))
+        else:
+            source = r.choice(lenders) if lenders and r.random() < 0.5 else None
+            if source is None:
+                lenders.append(i)
+            dim = r.choice([16, 32, 48, 64])
+            layer = latent(r.choice([2, 4, 6, 8]), dim, rot_dim, r.choice([16, 32, 64]), kv_rank, r.choice([48, 96, 128, 192]),
+                           kv_from=source, base=base, scaling=scaling, scale=r.choice([0.125, (dim + rot_dim) ** -0.5, 0.2]))
+        if r.random() < 0.1:
+            layers.append(with_moe(layer))
+        else:
+            shared = None if r.random() < 0.15 else (r.choice([64, 96, 128, 192]), r.choice([1.0, 2.0, 5.0]))
+            layers.append(with_moe(layer, experts=r.choice([4, 8, 12, 16]), identity=r.choice([0, 2, 4, 6]), top=r.choice([1, 2, 3, 4]),
+                                   ff=r.choice([32, 64, 96, 128]), limit=r.choice([1.0, 2.0, 4.0, 7.0]), shared=shared))
+    return model(width, vocab, r.choice([1e-6, 1e-5]), layers)
+
+
 # standard deviation of the random matrices: rows are of unit size behind the norm, and larger weights
 # make every softmax a choice of one key (the tests that want that ask for it)
 INIT_STD = 0.15

@@ -392,6 +392,39 @@ def test_whole_models_in_every_cutting(zoo, model, plan_name, dtype):
         assert runner.graphs.replays > 100               # decoded tokens ran as recorded steps
 
 
+@pytest.mark.parametrize("seed", [1, 4, 12])
+def test_configurations_drawn_from_a_seed(zoo, seed):
+    """Larger models of sizes nobody chose (see ``kemirax_models.random_config``), stored without the rank of the
+    decay's map (it is the tensors' own), in float32: five requests of up to 520 tokens on four slots, portions of
+    some beside single tokens of others.  How far float32 rounding moves the logits depends on the drawn weights
+    (ten or twelve layers of random matrices amplify it, and a router's close call, a gap between two choice scores
+    below the rounding of a sum, changes a row and, through a linear layer's state, hundreds after it), so the bound
+    is what the plain implementation itself loses when it runs in float32: the engine may lose twice that."""
+    config = M.random_config(seed)
+    folder, requests, want = zoo(config, "float32", [70, 520, 37, 150, 260], seed=seed, key=f"drawn{seed}")
+    stored = json.loads((folder / "config.json").read_text())
+    for layer in stored["layers"]:
+        layer["mixer"].pop("decay_rank", None)
+    (folder / "config.json").write_text(json.dumps(stored))
+
+    def spread(rows):
+        errors = [float((got - want[uid][pos]).abs().max()) / (1.0 + float(want[uid].abs().max())) for (uid, pos), got in rows.items()]
+        errors = torch.tensor(errors).sort().values
+        return float(errors[len(errors) // 2]), float(errors[int(0.97 * len(errors))])
+
+    plain32 = {u: plain.model_logits(folder, t, torch.float32) for u, t in requests.items()}
+    allowed = spread({(u, p): plain32[u][p] for u, t in requests.items() for p in range(len(t))})
+    assert allowed[0] < 1e-4                                   # (the drawn model is not beyond float32 altogether)
+    for plan_name in ("whole", "mixed"):
+        steps = PLANS[plan_name](requests) if plan_name == "whole" else H.plan_mixed(requests, max_live=4)
+        runner = make_runner(folder, "float32", 16, steps, max_live=4)
+        rows = H.run_plan(runner, steps)
+        assert len(rows) == sum(len(t) for t in requests.values())
+        median, bulk = spread(rows)
+        assert median <= 2 * allowed[0] + 2e-6 and bulk <= 2 * allowed[1] + 1e-5, (seed, plan_name, median, bulk, allowed)
+        runner.cache.audit()
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_sublayers_on_streams_of_their_own_give_the_bits_of_sublayers_in_turn(zoo, dtype):
     """In steps of few tokens the feed-forward and the gates' product run on streams of their own beside the mixer
