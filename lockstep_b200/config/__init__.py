@@ -11,9 +11,11 @@ from . import malazen as _malazen  # registers Malazen
 from .malazen import MalazenConfig
 from . import kemirax as _kemirax  # registers Kemirax
 from .kemirax import KemiraxConfig
+from . import pikurax as _pikurax  # registers Pikurax
+from .pikurax import PikuraxConfig
 
 __all__ = [
-    "ConfigError", "KemiraxConfig", "LayerRun", "LayerSpec", "MalazenConfig", "ModelSpec", "PartSpec", "Qwen3Config", "SevipelConfig",
+    "ConfigError", "KemiraxConfig", "LayerRun", "LayerSpec", "MalazenConfig", "ModelSpec", "PartSpec", "PikuraxConfig", "Qwen3Config", "SevipelConfig",
     "architecture_name", "config_from_dict", "known_architectures", "load_config",
     "own_tensors", "register_architecture", "tensor_name", "unregister_architecture",
 ]

@@ -72,6 +72,8 @@ class LayerRun:
     ``part`` of this run's cache is not its own but the same part of cache entry ``entry``, which
     an earlier run wrote, and is only read (a layer that attends over another layer's keys and
     values but carries a state of its own besides).
+    ``inject``: the model's injection part (``ModelSpec.injection``) runs on the residual stream right before this
+    run (a model that feeds the embedding's output in again through a projection at the start of every pass).
     """
 
     layer: int
@@ -79,6 +81,7 @@ class LayerRun:
     writes_cache: bool = True
     add_embedding: bool = False
     borrows: tuple = ()
+    inject: bool = False
 
 
 @dataclass(frozen=True)
@@ -98,6 +101,9 @@ class ModelSpec:
     # tensors a model folder may hold although this model reads none of them (say, the norm in
     # front of a feed-forward that the layer does not have)
     optional_tensors: tuple[str, ...] = ()
+    # a part that mixes the embedding's output into the residual stream where the schedule says so
+    # (``LayerRun.inject``); its tensors lie under ``names["injection"]``
+    injection: PartSpec | None = None
 
     def __post_init__(self):
         object.__setattr__(self, "names", _freeze(self.names))
@@ -106,6 +112,8 @@ class ModelSpec:
         object.__setattr__(self, "optional_tensors", tuple(self.optional_tensors))
         writers: dict[int, int] = {}
         for run in self.schedule:
+            if run.inject and self.injection is None:
+                raise ValueError("the schedule injects the embedding's output, but the model has no injection part")
             if not 0 <= run.layer < len(self.layers):
                 raise ValueError(f"schedule names layer {run.layer}, the model has {len(self.layers)}")
             for part, entry in run.borrows:
@@ -126,11 +134,16 @@ class ModelSpec:
 def tensor_name(prefix: str, local: str) -> str:
     """The full name of a part's tensor: a part may name a tensor "" to own its prefix itself
     (an embedding stored as ``embed`` rather than ``embed.weight``)."""
+    if not prefix:
+        return local        # a part without a prefix names its tensors itself
     return f"{prefix}.{local}" if local else prefix
 
 
 def own_tensors(prefix: str, tensors: Mapping[str, Any]) -> dict[str, Any]:
-    """The entries of ``tensors`` that lie under ``prefix``, by their local names."""
+    """The entries of ``tensors`` that lie under ``prefix``, by their local names (all of them for a part without
+    a prefix)."""
+    if not prefix:
+        return dict(tensors)
     out = {k[len(prefix) + 1:]: v for k, v in tensors.items() if k.startswith(prefix + ".")}
     if prefix in tensors:
         out[""] = tensors[prefix]

@@ -76,7 +76,7 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap map, const __nv_
   const int group = nq / nkv;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int* table_row = block_table + (int64_t)req_row * table_stride;
-  const int row_lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  const int row_lo = ls_first_key(pos, window);
   const int s_lo = split * LS_SPLIT;
   int s_hi = s_lo + LS_SPLIT;
   if (s_hi > pos + 1) s_hi = pos + 1;

@@ -216,7 +216,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     I.table_row = block_table + (int64_t)w[0] * table_stride;
     I.kvh = I.h / (nq / nkv);
     I.pos_last = I.pos0 + I.ntok - 1;
-    I.key_lo = (window > 0 && I.pos0 - window + 1 > 0) ? I.pos0 - window + 1 : 0;   // first key any row reads
+    I.key_lo = ls_first_key(I.pos0, window);   // first key any row reads
     I.tile_first = I.key_lo / BLOCK_N;
     I.n_tiles = I.pos_last / BLOCK_N + 1 - I.tile_first;
     return 1;
@@ -422,8 +422,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       if (kind == 2) continue;
       const int pos0 = I.pos0, pos_last = I.pos_last, tile_first = I.tile_first, n_tiles = I.n_tiles;
       const int pos = pos0 + row;
-      const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-      const int lo_last = (window > 0 && pos_last - window + 1 > 0) ? pos_last - window + 1 : 0;
+      const int lo = ls_first_key(pos, window);
+      const int lo_last = ls_first_key(pos_last, window);
       float m_ref = -CUDART_INF_F, l_run = 0.f;
       float bias_a = 0.f, bias_b = 0.f;
       bool biased = false;
@@ -677,7 +677,7 @@ attention_prefill_tc_pair_kernel(const __grid_constant__ CUtensorMap map_q, cons
     I.table_row = block_table + (int64_t)w[0] * table_stride;
     I.kvh = I.h / (nq / nkv);
     I.pos_last = I.pos0 + I.ntok - 1;
-    I.key_lo = (window > 0 && I.pos0 - window + 1 > 0) ? I.pos0 - window + 1 : 0;
+    I.key_lo = ls_first_key(I.pos0, window);
     I.tile_first = I.key_lo / BLOCK_N;
     I.n_tiles = I.pos_last / BLOCK_N + 1 - I.tile_first;
     return 1;
@@ -887,8 +887,8 @@ attention_prefill_tc_pair_kernel(const __grid_constant__ CUtensorMap map_q, cons
       if (kind == 2) continue;
       const int pos0 = I.pos0, pos_last = I.pos_last, tile_first = I.tile_first, n_tiles = I.n_tiles;
       const int pos = pos0 + row;
-      const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-      const int lo_last = (window > 0 && pos_last - window + 1 > 0) ? pos_last - window + 1 : 0;
+      const int lo = ls_first_key(pos, window);
+      const int lo_last = ls_first_key(pos_last, window);
       // the sum of a row's weights is kept per quarter of a tile's keys (32 sub .. + 31), as the
       // kernel with four threads a row keeps it, so that both give the same bits
       float m_ref = -CUDART_INF_F, l_run[2] = {0.f, 0.f};

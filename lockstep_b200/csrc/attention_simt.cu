@@ -55,7 +55,7 @@ attention_tile_kernel(const T* __restrict__ q, const T* __restrict__ pages, T* _
                       float* __restrict__ part_acc, float* __restrict__ part_ml,
                       const int* __restrict__ work, const int* __restrict__ block_table,
                       int table_stride, int nq, int nkv, int d, int page_size, int num_pages,
-                      int window, float scale, const float* __restrict__ slopes,
+                      int window, float scale, float softcap, const float* __restrict__ slopes,
                       const float* __restrict__ log_rates, const float* __restrict__ sinks, int hb, int* err) {
   ls_dependency_sync();
   extern __shared__ __align__(16) float smem[];
@@ -88,10 +88,10 @@ attention_tile_kernel(const T* __restrict__ q, const T* __restrict__ pages, T* _
   const int* table_row = block_table + (int64_t)req_row * table_stride;
 
   const int pos_last = pos0 + ntok - 1;
-  const int key_lo_tile = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
+  const int key_lo_tile = ls_first_key(pos0, window);
   const int qpos = pos0 + m_tok;
   const bool row_valid = m < ntok * heads_at_once;
-  const int row_lo = (window > 0 && qpos - window + 1 > 0) ? qpos - window + 1 : 0;
+  const int row_lo = ls_first_key(qpos, window);
 
   for (int h_first = (int)blockIdx.y * hb; h_first < ((int)blockIdx.y + 1) * hb; h_first += heads_at_once) {
   const int h = h_first + m - m_tok * heads_at_once;           // this row's head
@@ -193,8 +193,8 @@ attention_tile_kernel(const T* __restrict__ q, const T* __restrict__ pages, T* _
           const int key = n0 + sub + 8 * j;
           const bool keep = key < s_hi && key <= qpos && key >= row_lo;
           s[j] = !keep ? -CUDART_INF_F
-                 : log_rates != nullptr ? dot[j] * scale - slope * log1pf(log_rate * (float)(qpos - key))
-                 : slopes != nullptr ? fmaf(slope, (float)(key - qpos), dot[j] * scale) : dot[j] * scale;
+                 : log_rates != nullptr ? ls_capped(dot[j] * scale, softcap) - slope * log1pf(log_rate * (float)(qpos - key))
+                 : slopes != nullptr ? fmaf(slope, (float)(key - qpos), ls_capped(dot[j] * scale, softcap)) : ls_capped(dot[j] * scale, softcap);
           tile_max = fmaxf(tile_max, s[j]);
         }
       }
@@ -317,7 +317,7 @@ attention_decode_kernel(const T* __restrict__ q, const T* __restrict__ pages,
                         float* __restrict__ part_acc, float* __restrict__ part_ml,
                         const int* __restrict__ work, const int* __restrict__ block_table,
                         int table_stride, int nq, int nkv, int d, int page_size, int num_pages,
-                        int window, float scale, const float* __restrict__ slopes,
+                        int window, float scale, float softcap, const float* __restrict__ slopes,
                         const float* __restrict__ log_rates, int slot_limit, int* err) {
   ls_dependency_sync();
   extern __shared__ __align__(16) unsigned char dsm[];
@@ -344,7 +344,7 @@ attention_decode_kernel(const T* __restrict__ q, const T* __restrict__ pages,
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int* table_row = block_table + (int64_t)req_row * table_stride;
 
-  const int row_lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  const int row_lo = ls_first_key(pos, window);
   const int s_lo = split * LS_SPLIT;
   int s_hi = s_lo + LS_SPLIT;
   if (s_hi > pos + 1) s_hi = pos + 1;
@@ -398,8 +398,8 @@ attention_decode_kernel(const T* __restrict__ q, const T* __restrict__ pages,
       }
       const bool keep = key < s_hi && key >= row_lo;
       Ss[u] = !keep ? -CUDART_INF_F
-              : log_rates != nullptr ? dot * scale - slopes[kvh * group + g] * log1pf(log_rates[kvh * group + g] * (float)(pos - key))
-              : slopes != nullptr ? fmaf(slopes[kvh * group + g], (float)(key - pos), dot * scale) : dot * scale;
+              : log_rates != nullptr ? ls_capped(dot * scale, softcap) - slopes[kvh * group + g] * log1pf(log_rates[kvh * group + g] * (float)(pos - key))
+              : slopes != nullptr ? fmaf(slopes[kvh * group + g], (float)(key - pos), ls_capped(dot * scale, softcap)) : ls_capped(dot * scale, softcap);
     }
     __syncthreads();
 
@@ -501,7 +501,7 @@ LS_API int ls_attention_split_size() { return LS_SPLIT; }
 LS_API int ls_attention_tile(const void* q, const void* pages, void* out, float* part_acc,
                              float* part_ml, int dtype, const int* work, int n_work,
                              const int* block_table, int table_stride, int nq, int nkv, int d,
-                             int page_size, int num_pages, int window, float scale,
+                             int page_size, int num_pages, int window, float scale, float softcap,
                              const float* slopes, const float* log_rates, const float* sinks, int* err,
                              cudaStream_t stream) {
   if (n_work <= 0) return 0;
@@ -526,7 +526,7 @@ LS_API int ls_attention_tile(const void* q, const void* pages, void* out, float*
     if (smem > set_f32) set_f32 = smem;
     LS_COUNT(LS_K_ATTENTION_TILE), ls_launch(attention_tile_kernel<float>, grid, 128, smem, stream, 
         (const float*)q, (const float*)pages, (float*)out, part_acc, part_ml, work, block_table,
-        table_stride, nq, nkv, d, page_size, num_pages, window, scale, slopes, log_rates, sinks, hb, err);
+        table_stride, nq, nkv, d, page_size, num_pages, window, scale, softcap, slopes, log_rates, sinks, hb, err);
   } else if (dtype == LS_BF16) {
     e = smem <= set_bf16 ? cudaSuccess
                          : cudaFuncSetAttribute(attention_tile_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -535,7 +535,7 @@ LS_API int ls_attention_tile(const void* q, const void* pages, void* out, float*
     LS_COUNT(LS_K_ATTENTION_TILE), ls_launch(attention_tile_kernel<__nv_bfloat16>, grid, 128, smem, stream, 
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)pages, (__nv_bfloat16*)out, part_acc,
         part_ml, work, block_table, table_stride, nq, nkv, d, page_size, num_pages, window, scale,
-        slopes, log_rates, sinks, hb, err);
+        softcap, slopes, log_rates, sinks, hb, err);
   } else {
     return LS_E_DTYPE;
   }
@@ -548,7 +548,7 @@ namespace {
 int launch_attention_decode(const void* q, const void* pages, float* part_acc, float* part_ml,
                             int dtype, const int* work, int n_work, const int* block_table,
                             int table_stride, int nq, int nkv, int d, int page_size,
-                            int num_pages, int window, float scale, const float* slopes,
+                            int num_pages, int window, float scale, float softcap, const float* slopes,
                             const float* log_rates, int slot_limit, int* err, cudaStream_t stream) {
   if (n_work <= 0) return 0;
   if (log_rates != nullptr && slopes == nullptr) return LS_E_SIZE;
@@ -566,7 +566,7 @@ int launch_attention_decode(const void* q, const void* pages, float* part_acc, f
     if (smem > set_f32) set_f32 = smem;
     LS_COUNT(LS_K_ATTENTION_DECODE), ls_launch(attention_decode_kernel<float>, grid, 128, smem, stream, 
         (const float*)q, (const float*)pages, part_acc, part_ml, work, block_table, table_stride,
-        nq, nkv, d, page_size, num_pages, window, scale, slopes, log_rates, slot_limit, err);
+        nq, nkv, d, page_size, num_pages, window, scale, softcap, slopes, log_rates, slot_limit, err);
   } else if (dtype == LS_BF16) {
     const size_t smem = decode_smem_bytes(d, group, 2);
     e = smem <= set_bf16 ? cudaSuccess
@@ -575,7 +575,7 @@ int launch_attention_decode(const void* q, const void* pages, float* part_acc, f
     if (smem > set_bf16) set_bf16 = smem;
     LS_COUNT(LS_K_ATTENTION_DECODE), ls_launch(attention_decode_kernel<__nv_bfloat16>, grid, 128, smem, stream, 
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)pages, part_acc, part_ml, work,
-        block_table, table_stride, nq, nkv, d, page_size, num_pages, window, scale, slopes, log_rates, slot_limit, err);
+        block_table, table_stride, nq, nkv, d, page_size, num_pages, window, scale, softcap, slopes, log_rates, slot_limit, err);
   } else {
     return LS_E_DTYPE;
   }
@@ -605,10 +605,10 @@ int launch_attention_combine(const float* part_acc, const float* part_ml, void* 
 LS_API int ls_attention_decode(const void* q, const void* pages, float* part_acc, float* part_ml,
                                int dtype, const int* work, int n_work, const int* block_table,
                                int table_stride, int nq, int nkv, int d, int page_size,
-                               int num_pages, int window, float scale, const float* slopes,
+                               int num_pages, int window, float scale, float softcap, const float* slopes,
                                const float* log_rates, int* err, cudaStream_t stream) {
   return launch_attention_decode(q, pages, part_acc, part_ml, dtype, work, n_work, block_table, table_stride, nq,
-                                 nkv, d, page_size, num_pages, window, scale, slopes, log_rates, 0, err, stream);
+                                 nkv, d, page_size, num_pages, window, scale, softcap, slopes, log_rates, 0, err, stream);
 }
 
 LS_API int ls_attention_combine(const float* part_acc, const float* part_ml, void* out, int dtype,
@@ -671,7 +671,7 @@ LS_API int ls_attention_decode_noalloc(const void* q, const void* pages, void* o
   // in the error word (LS_DEV_ROW_RANGE) and skipped, it cannot write outside the array
   const int status = launch_attention_decode(q, pages, part_acc, part_ml, dtype, work, n_work,
                                              block_table, table_stride, nq, nkv, d, page_size,
-                                             num_pages, window, scale, nullptr, nullptr, n_slots, err, stream);
+                                             num_pages, window, scale, 0.f, nullptr, nullptr, n_slots, err, stream);
   if (status != 0) return status;
   return launch_attention_combine(part_acc, part_ml, out, dtype, combine, n_combine, nq, d, n_slots, nullptr, err, stream);
 }

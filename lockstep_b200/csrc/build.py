@@ -31,11 +31,11 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC"]
 # library name -> sources.  "core" holds the kernels that take every size; the
 # others hold the tensor-core kernels for the sizes they are specialised for.
 LIBRARIES: dict[str, list[str]] = {
-    "core": ["elementwise.cu", "gemm_simt.cu", "attention_simt.cu", "sampling.cu"],
+    "core": ["elementwise.cu", "rowwise.cu", "gemm_simt.cu", "attention_simt.cu", "sampling.cu"],
     "tc": ["gemm_tc.cu", "attention_decode_mma.cu", "attention_prefill_tc.cu"],
     # mixers with a carried state, routed experts, projections with heads of unequal sizes:
     # loaded when a model first builds a part that needs them
-    "seq": ["heads_wide.cu", "recurrent.cu", "experts.cu", "experts_tc.cu", "latent.cu"],
+    "seq": ["heads_wide.cu", "recurrent.cu", "unit_recurrence.cu", "experts.cu", "experts_tc.cu", "latent.cu"],
 }
 
 _HEADERS = ["common.cuh", "tc_common.cuh", "no_alloc.h", "rope.cuh", "attention_fold.cuh"]

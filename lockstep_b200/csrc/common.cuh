@@ -73,6 +73,8 @@ enum LsKernelId {
   LS_K_EXPERTS_GATHER, LS_K_EXPERTS_UP_TC, LS_K_EXPERTS_DOWN_TC, LS_K_TANH, LS_K_DOUBLE_EXP_DECAY,
   LS_K_CLAMPED_GLU, LS_K_ROW_BIAS, LS_K_WEIGHTED_SUM, LS_K_GLA_RULE, LS_K_SIGMOID_POWER_DECAY, LS_K_LATENT_FINISH,
   LS_K_HEADS_PRODUCT, LS_K_GATED_SUM, LS_K_EXPERTS_MIX, LS_K_RMSNORM_SHIFT,
+  LS_K_LAYERNORM, LS_K_NORM_MERGE_ADD, LS_K_PAIR_EMBED, LS_K_ROWS_CAST, LS_K_SCALE_CAP, LS_K_UNIT_GATES, LS_K_UNIT_SCAN,
+  LS_K_ROTATE_ROWS,
   LS_K_COUNT
 };
 #define LS_KERNEL_NAMES                                                                                  \
@@ -83,7 +85,8 @@ enum LsKernelId {
   "wkv_rule,head_rms_gate,experts_route,experts_plan,experts_up,experts_down,experts_combine,"     \
   "experts_gather,experts_up_tc,experts_down_tc,tanh_rows,double_exp_decay,"                      \
   "clamped_glu,row_bias,weighted_sum,gla_rule,sigmoid_power_decay,latent_finish,heads_product,"  \
-  "gated_sum,experts_mix,rmsnorm_shift"
+  "gated_sum,experts_mix,rmsnorm_shift,layernorm,norm_merge_add,pair_embed,rows_cast,scale_cap,unit_gates,"                 \
+  "unit_scan,rotate_rows"
 // one table per library: hidden, so that two libraries loaded into one process do not share it
 __attribute__((visibility("hidden"))) inline unsigned long long ls_kernel_launches[LS_K_COUNT];
 #define LS_COUNT(id) (++ls_kernel_launches[id])
@@ -131,6 +134,20 @@ __device__ __forceinline__ float ls_block_sum(float v, float* scratch) {
   float total = 0.f;
   for (int w = 0; w < nwarps; ++w) total += scratch[w];
   return total;
+}
+
+// The first key position a query at `pos` reads: window > 0, the last `window` positions (a sliding
+// window); window < 0, the positions of the query's own chunk of -window positions, chunks counted
+// from position 0 of the sequence; 0, every earlier position.  It never falls as `pos` grows.
+__host__ __device__ __forceinline__ int ls_first_key(int pos, int window) {
+  if (window > 0) return pos - window + 1 > 0 ? pos - window + 1 : 0;
+  if (window < 0) return pos - pos % (-window);
+  return 0;
+}
+
+// cap x tanh(score / cap) where a cap is given (cap > 0), else the score itself
+__device__ __forceinline__ float ls_capped(float score, float cap) {
+  return cap > 0.f ? cap * tanhf(score / cap) : score;
 }
 
 // Programmatic dependent launch: a kernel may be scheduled while its predecessor

@@ -435,7 +435,8 @@ LS_API int ls_silu_mul(const void* gate_up, void* out, int dtype, int rows, int 
 template <typename TI, typename TO, typename TB>
 __global__ void clamped_glu_kernel(const TI* __restrict__ gate_up, const TB* __restrict__ bias, TO* __restrict__ out,
                                    int64_t rows, int width, int64_t in_ld, float limit, float alpha,
-                                   float* __restrict__ residual, const TB* __restrict__ res_bias, int res_width, int vec) {
+                                   float* __restrict__ residual, const TB* __restrict__ res_bias, int res_width, int vec,
+                                   float up_offset, int gelu) {
   ls_dependency_sync();
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   auto act = [&](float g, float u, int c) {
@@ -445,7 +446,9 @@ __global__ void clamped_glu_kernel(const TI* __restrict__ gate_up, const TB* __r
     }
     g = fminf(g, limit);
     u = fminf(fmaxf(u, -limit), limit);
-    return g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
+    // gelu: the tanh form, 0.5 g (1 + tanh(sqrt(2 / pi) (g + 0.044715 g^3)))
+    if (gelu) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * (u + up_offset);
+    return g / (1.0f + expf(-alpha * g)) * (u + up_offset);
   };
   if (vec) {
     // four columns a thread, 16 bytes a load (widths that are multiples of four, aligned rows)
@@ -476,7 +479,7 @@ __global__ void clamped_glu_kernel(const TI* __restrict__ gate_up, const TB* __r
 
 LS_API int ls_clamped_glu(const void* gate_up, long long in_ld, int in_dtype, const void* bias, int bias_dtype, void* out,
                           int out_dtype, int rows, int width, float limit, float alpha, float* residual,
-                          const void* res_bias, int res_width, cudaStream_t stream) {
+                          const void* res_bias, int res_width, float up_offset, int gelu, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (width <= 0 || in_ld < 2 * (long long)width || (residual != nullptr && (res_bias == nullptr || res_width <= 0)))
     return LS_E_SIZE;
@@ -489,7 +492,7 @@ LS_API int ls_clamped_glu(const void* gate_up, long long in_ld, int in_dtype, co
   LS_COUNT(LS_K_CLAMPED_GLU);
 #define LS_GLU(TI, TO, TB)                                                                                        \
   ls_launch(clamped_glu_kernel<TI, TO, TB>, blocks, 256, 0, stream, (const TI*)gate_up, (const TB*)bias, (TO*)out, \
-            (int64_t)rows, width, (int64_t)in_ld, limit, alpha, residual, (const TB*)res_bias, res_width, vec)
+            (int64_t)rows, width, (int64_t)in_ld, limit, alpha, residual, (const TB*)res_bias, res_width, vec, up_offset, gelu)
   if (in_dtype == LS_F32 && out_dtype == LS_F32 && bias_dtype == LS_F32) LS_GLU(float, float, float);
   else if (in_dtype == LS_F32 && out_dtype == LS_BF16 && bias_dtype == LS_BF16) LS_GLU(float, __nv_bfloat16, __nv_bfloat16);
   else if (in_dtype == LS_F32 && out_dtype == LS_BF16 && bias_dtype == LS_F32) LS_GLU(float, __nv_bfloat16, float);

@@ -36,7 +36,9 @@ __device__ __forceinline__ void route_token(const float* __restrict__ logits, in
     const int e = lane + 32 * i;
     z[i] = e < experts ? logits[(int64_t)t * ld + e] : -INFINITY;
   }
-  if (softmax) {
+  if (softmax == 2) {
+    // the scores are the logits themselves; the weights become a softmax over the chosen ones below
+  } else if (softmax) {
     float top_z = -INFINITY;
 #pragma unroll
     for (int i = 0; i < MAX_PER_LANE; ++i) top_z = fmaxf(top_z, z[i]);
@@ -87,6 +89,17 @@ __device__ __forceinline__ void route_token(const float* __restrict__ logits, in
       ids[(int64_t)t * top + r] = at;
       weights[(int64_t)t * top + r] = best_z;
     }
+  }
+  if (softmax == 2 && lane == 0) {
+    // softmax over the chosen logits alone (the first is the largest), summed in order of rank
+    float* w = weights + (int64_t)t * top;
+    const float top_z = w[0];
+    float sum = 0.f;
+    for (int r = 0; r < top; ++r) {
+      w[r] = expf(w[r] - top_z);
+      sum += w[r];
+    }
+    for (int r = 0; r < top; ++r) w[r] = w[r] / sum;
   }
 }
 

@@ -240,6 +240,7 @@ struct RuleArgs {
   int H, G, dk, dv, lanes; // lanes: threads that share a column (a power of two, lanes * ROWS >= dk)
   int64_t in_ld;           // gla: q, k, v are columns of wider rows, this many elements apart
   float out_scale;         // gla: factor on the read-out (the queries' scale)
+  int64_t decay_ld;        // elements between two tokens' decays (H dk), or 0: one decay [H dk] for every token
 };
 
 // One staged value's source: where token t's copy lies (p + t * stride), and its element type.
@@ -296,7 +297,7 @@ __global__ void __launch_bounds__(128) rule_kernel(RuleArgs a) {
       const int which = k / dk, i = k - which * dk;
       if (which == 2) {
         s.p = reinterpret_cast<const char*>(a.decay + h * dk + i);
-        s.stride = (int64_t)a.H * dk * 4;
+        s.stride = a.decay_ld * 4;
         s.kind = 1;
       } else if (RULE == RULE_DELTA) {
         s.p = reinterpret_cast<const char*>(reinterpret_cast<const float*>(a.in_a) + which * Kd + g * dk + i);
@@ -622,7 +623,7 @@ LS_API int ls_state_rule(int rule, int dtype, const int* portions, int max_porti
                          const void* in_a, const void* in_b, const void* in_v, const float* decay,
                          const float* beta, const float* bonus, float* out, const void* carry_src, int64_t carry_ld, int carry_width,
                          int carry_rows, int H, int G, int dk, int dv, int64_t in_ld, float out_scale,
-                         cudaStream_t stream) {
+                         int64_t decay_ld, cudaStream_t stream) {
   if (max_portions <= 0) return 0;
   if (H <= 0 || G <= 0 || H % G || dk <= 0 || dk > 32 * ROWS || dv <= 0 || carry_rows < 0 || carry_rows >= MAX_TAPS) return LS_E_SIZE;
   if (H > 65535) return LS_E_SIZE;
@@ -632,6 +633,7 @@ LS_API int ls_state_rule(int rule, int dtype, const int* portions, int max_porti
   a.carry_width = carry_width; a.carry_rows = carry_rows; a.H = H; a.G = G; a.dk = dk; a.dv = dv;
   a.lanes = lanes_for(dk);
   a.in_ld = in_ld; a.out_scale = out_scale;
+  a.decay_ld = decay_ld < 0 ? (int64_t)H * dk : decay_ld;
   // columns a block: as many as fill 128 threads, fewer where the head has fewer
   int threads = 128;
   while (threads > 32 && (threads / 2) / a.lanes >= dv) threads /= 2;

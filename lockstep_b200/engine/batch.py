@@ -37,6 +37,16 @@ class AttentionPlan:
     n_slots: int
 
 
+def first_key(pos, window: int):
+    """The first key position a query at ``pos`` (a number or an array) reads: the last ``window`` positions
+    (window > 0), the query's own chunk of -window positions counted from position 0 (window < 0), or all (0)."""
+    if window > 0:
+        return np.maximum(0, pos - window + 1) if isinstance(pos, np.ndarray) else max(0, pos - window + 1)
+    if window < 0:
+        return pos - pos % (-window)
+    return pos * 0
+
+
 def plan_attention(portions, window: int, split_size: int, tile_tokens: int = TILE_TOKENS):
     """portions: (slot, token offset, start position, length) per entry.
     Returns numpy arrays (tile_work [n,8], split_work [n,8], combine [n,4]) and
@@ -46,7 +56,7 @@ def plan_attention(portions, window: int, split_size: int, tile_tokens: int = TI
     n_slots = 0
     for slot, off, start, length in portions:
         if length == 1:
-            lo = max(0, start - window + 1) if window else 0
+            lo = first_key(start, window)
             s_lo, s_hi = lo // split_size, start // split_size
             combine.append((off, n_slots, 1, s_hi - s_lo + 1))
             for s in range(s_lo, s_hi + 1):
@@ -56,7 +66,7 @@ def plan_attention(portions, window: int, split_size: int, tile_tokens: int = TI
             for i in range(0, length, tile_tokens):
                 ntok = min(tile_tokens, length - i)
                 pos0 = start + i
-                lo = max(0, pos0 - window + 1) if window else 0
+                lo = first_key(pos0, window)
                 tile.append((slot, off + i, ntok, pos0, lo // split_size,
                              (pos0 + ntok - 1) // split_size + 1, -1, 0))
     tile.sort(key=lambda item: -(item[3] + item[2]))

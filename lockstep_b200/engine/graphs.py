@@ -36,7 +36,7 @@ from collections import OrderedDict
 import numpy as np
 import torch
 
-from .batch import AttentionPlan, plan_attention
+from .batch import AttentionPlan, first_key, plan_attention
 
 CAPACITY_STEP = 32      # the attention work list of a recorded step holds a multiple of this many items
 MAX_GRAPHS = 24         # recorded steps kept; the least recently used one goes first
@@ -109,7 +109,7 @@ class StaticStepContext:
         h[3 * b:4 * b] = self._arange
         for w in self.windows:
             # one item per (entry, split): splits lo // S .. start // S of each entry, in entry order
-            lo = np.maximum(0, start - w + 1) if w else np.zeros(b, dtype=np.int64)
+            lo = first_key(start, w)
             first, last = lo // self.split_size, start // self.split_size
             count = last - first + 1
             count[n:] = 0                  # padding rows attend to nothing: no items, an empty combine
@@ -242,7 +242,7 @@ def split_items(entries, windows: list[int], split_size: int) -> int:
     for w in windows:
         n = 0
         for e in entries:
-            lo = max(0, e.start - w + 1) if w else 0
+            lo = first_key(e.start, w)
             n += e.start // split_size - lo // split_size + 1
         worst = max(worst, n)
     return worst

@@ -24,6 +24,11 @@ class Model:
         self.final_norm = build_part("norm", spec.final_norm, runtime)
         self.head = build_part("head", spec.head, runtime)
         self.tied_head = bool(getattr(self.head, "tied", False))
+        self.injection = build_part("injection", spec.injection, runtime) if spec.injection is not None else None
+        # an embedding that keeps something per request (the token before a portion) has a cache entry of its own,
+        # after the schedule's
+        need = getattr(self.embedding, "cache_need", lambda: None)()
+        self.embedding_entry = spec.cache_entries if need is not None else None
 
     # -- weights ------------------------------------------------------------
     def _named_parts(self):
@@ -33,6 +38,8 @@ class Model:
             yield layer.prefix, block
         yield n["final_norm"], self.final_norm
         yield n["head"], self.head
+        if self.injection is not None:
+            yield n["injection"], self.injection
 
     def weight_specs(self) -> dict[str, WeightSpec]:
         out: dict[str, WeightSpec] = {}
@@ -83,6 +90,8 @@ class Model:
                 parts = list(lender.parts)
                 parts[part] = parts[part].widened(reader)
                 needs[entry] = replace(lender, parts=tuple(parts))
+        if self.embedding_entry is not None:
+            needs.append(self.embedding.cache_need())
         return needs
 
 

@@ -116,7 +116,17 @@ class ModelRunner:
         model = self.model
 
         def embed(h, ctx):
-            return model.embedding.forward(ctx)
+            if model.embedding_entry is not None:
+                h = model.embedding.forward(ctx, self.cache.view(model.embedding_entry))
+            else:
+                h = model.embedding.forward(ctx)
+            if model.injection is not None:
+                model.injection.keep(ctx, h)
+            return h
+
+        def inject(h, ctx):
+            model.injection.forward(h, ctx)
+            return h
 
         def layer_step(fn, run):
             def call(h, ctx):
@@ -133,8 +143,10 @@ class ModelRunner:
             model.embedding.accumulate(h, ctx)
             return h
 
-        program = [(bool(model.embedding.graph_safe), embed)]
+        program = [(bool(model.embedding.graph_safe and (model.injection is None or model.injection.graph_safe)), embed)]
         for run in self.spec.schedule:
+            if run.inject:
+                program.append((bool(model.injection.graph_safe), inject))
             if run.add_embedding:
                 program.append((bool(model.embedding.graph_safe), add_embedding))
             for safe, fn in model.blocks[run.layer].steps():

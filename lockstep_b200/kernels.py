@@ -52,7 +52,14 @@ _SIGNATURES = {
         "ls_gated_sum": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p,
                          ctypes.c_longlong, c_void_p, c_void_p],
         "ls_clamped_glu": [c_void_p, ctypes.c_longlong, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_float,
-                           c_void_p, c_void_p, c_int, c_void_p],
+                           c_void_p, c_void_p, c_int, c_float, c_int, c_void_p],
+        "ls_layernorm": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
+        "ls_norm_merge_add": [c_void_p, c_void_p, c_int, ctypes.c_longlong, c_void_p, c_float, c_void_p, c_int, c_int, c_float,
+                              c_float, c_void_p],
+        "ls_pair_embed": [c_void_p, c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
+                          c_int, c_int, ctypes.c_longlong, ctypes.c_longlong, c_float, c_void_p, c_void_p],
+        "ls_rows_cast": [c_void_p, c_void_p, c_int, ctypes.c_longlong, c_int, ctypes.c_longlong, c_void_p],
+        "ls_scale_cap": [c_void_p, ctypes.c_longlong, c_float, c_float, c_void_p],
         "ls_row_bias": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
         "ls_weighted_sum": [c_void_p, c_void_p, ctypes.c_longlong, c_int, ctypes.POINTER(c_float), c_void_p, c_int,
                             c_void_p],
@@ -66,9 +73,9 @@ _SIGNATURES = {
         "ls_attention_split_size": [],
         "ls_attention_tile": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                               c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                              c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+                              c_float, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
         "ls_attention_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
-                                c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                                c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float,
                                 c_void_p, c_void_p, c_void_p, c_void_p],
         "ls_attention_combine": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
                                  c_void_p, c_void_p],
@@ -114,7 +121,14 @@ _SIGNATURES["seq"] = {
                      c_void_p],
     "ls_state_rule": [c_int, c_int, c_void_p, c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
                       c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_int,
-                      c_int64, c_float, c_void_p],
+                      c_int64, c_float, c_int64, c_void_p],
+    "ls_unit_gates": [c_void_p, ctypes.c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, ctypes.c_longlong,
+                      c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                      c_int, c_float, c_void_p],
+    "ls_unit_scan": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, ctypes.c_longlong, c_int, c_int, c_int, c_void_p,
+                     c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_int, c_int, c_void_p],
+    "ls_rotate_rows": [c_void_p, ctypes.c_longlong, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                       c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
     "ls_head_rms_gate": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                          c_float, c_int64, c_void_p],
     "ls_tanh_rows": [c_void_p, c_int, ctypes.c_longlong, c_void_p],
@@ -380,8 +394,10 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
                                  _stream()), "silu_mul")
 
 
-def clamped_glu(gate_up, bias, out, limit: float, alpha: float, residual=None, residual_bias=None) -> None:
-    """out = g sigmoid(alpha g) (u + 1) with g = min(gate + b, limit), u = clamp(up + b, -limit, limit), from
+def clamped_glu(gate_up, bias, out, limit: float, alpha: float, residual=None, residual_bias=None,
+                up_offset: float = 1.0, gelu: bool = False) -> None:
+    """(``up_offset``: what is added to u, 1 unless given; ``gelu``: the tanh form of gelu of g in place of g sigmoid(alpha g).)
+    out = g sigmoid(alpha g) (u + 1) with g = min(gate + b, limit), u = clamp(up + b, -limit, limit), from
     ``gate_up`` [rows, 2 width] (gate columns, then up columns; float32 or the type of ``out``; a view of some
     columns of a wider tensor is fine) and ``bias`` [2 width] or None.  With ``residual`` (float32 [rows, w]) and ``residual_bias`` [w] the same launch adds the
     bias of the projection that follows into the residual stream."""
@@ -398,7 +414,8 @@ def clamped_glu(gate_up, bias, out, limit: float, alpha: float, residual=None, r
     _check(library().ls_clamped_glu(
         gp, g_ld, _code(gate_up), _opt(bias, "bias"), _code(some) if some is not None else F32,
         _dev(out, "out"), _code(out), rows, width, float(limit), float(alpha), _opt(residual, "residual", torch.float32),
-        _opt(residual_bias, "residual_bias"), residual.shape[1] if residual is not None else 0, _stream()), "clamped_glu")
+        _opt(residual_bias, "residual_bias"), residual.shape[1] if residual is not None else 0, float(up_offset),
+        1 if gelu else 0, _stream()), "clamped_glu")
 
 
 def row_bias(x, bias, add: bool = False) -> None:
@@ -421,6 +438,61 @@ def weighted_sum(residual, branches, scales, bias=None) -> None:
     _check(library().ls_weighted_sum(_dev(residual, "residual", torch.float32), _dev(branches, "branches", torch.float32),
                                      residual.numel(), n, (c_float * n)(*[float(v) for v in scales]),
                                      _opt(bias, "bias", torch.float32), residual.shape[-1], _stream()), "weighted_sum")
+
+
+def layernorm(x, gain, out, eps: float, err, row_index=None) -> None:
+    """out = (x - mean) rsqrt(var + eps) gain over float32 rows of ``x`` (all, or those ``row_index`` names)."""
+    rows, width = out.shape
+    if x.shape[1] != width or gain.numel() != width or (row_index is None and x.shape[0] != rows) \
+            or (row_index is not None and row_index.numel() != rows):
+        raise KernelError("layernorm: shapes do not agree")
+    _check(library().ls_layernorm(
+        _dev(x, "x", torch.float32), _opt(row_index, "row_index", torch.int32), _dev(gain, "gain"), _code(gain),
+        _dev(out, "out"), _code(out), rows, width, x.shape[0], float(eps), _dev(err, "err", torch.int32), _stream()), "layernorm")
+
+
+def norm_merge_add(residual, branches, branch_gain, scale: float, post_gain, eps_branch: float, eps_post: float) -> None:
+    """residual += post(scale sum_b rms(branches[b]) branch_gain[b]): ``branches`` float32 [n, rows, width]; with
+    ``branch_gain`` (float32 [n, width]) every branch is divided by its root mean square and multiplied by its gain,
+    without it the branches are summed as they are; ``post_gain`` (float32 [width]): the sum goes through a layer norm
+    with this gain before it is added."""
+    n, rows, width = branches.shape
+    if tuple(residual.shape) != (rows, width) or (branch_gain is not None and tuple(branch_gain.shape) != (n, width)) \
+            or (post_gain is not None and post_gain.numel() != width):
+        raise KernelError("norm_merge_add: shapes do not agree")
+    _check(library().ls_norm_merge_add(
+        _dev(residual, "residual", torch.float32), _dev(branches, "branches", torch.float32), n, rows * width,
+        _opt(branch_gain, "branch_gain", torch.float32), float(scale), _opt(post_gain, "post_gain", torch.float32),
+        rows, width, float(eps_branch), float(eps_post), _stream()), "norm_merge_add")
+
+
+def pair_embed(ids, token_slot, carried, table, pairs, out, factor: float, mul_prev: int, mul_cur: int, err) -> None:
+    """out[t] = table[ids[t]] factor + pairs[(previous id x mul_prev + ids[t] x mul_cur) mod buckets], the last row of
+    ``pairs`` [buckets + 1, width] for a request's first token; the previous id is the token in front where it belongs to
+    the same request, else what ``carried`` (int32 [slots, >= 1]: last token + 1) holds, which is then brought up to date.
+    Without ``pairs``: the scaled gather alone."""
+    tokens, width = out.shape
+    if ids.numel() != tokens or table.shape[1] != width or (pairs is not None and (pairs.shape[1] != width or pairs.dtype != table.dtype)):
+        raise KernelError("pair_embed: shapes do not agree")
+    _check(library().ls_pair_embed(
+        _dev(ids, "ids", torch.int32), _opt(token_slot, "token_slot", torch.int32), _opt(carried, "carried", torch.int32),
+        carried.stride(0) if carried is not None else 0, _dev(table, "table"), _opt(pairs, "pairs"), _code(table),
+        _dev(out, "out", torch.float32), tokens, width, table.shape[0], pairs.shape[0] - 1 if pairs is not None else 0,
+        int(mul_prev), int(mul_cur), float(factor), _dev(err, "err", torch.int32), _stream()), "pair_embed")
+
+
+def rows_cast(src, dst) -> None:
+    """dst = src (float32 [rows, width]) in the type of ``dst``, which may be some columns of a wider tensor."""
+    if src.shape != dst.shape:
+        raise KernelError("rows_cast: shapes do not agree")
+    dp, ld = _rows(dst, "dst")
+    _check(library().ls_rows_cast(_dev(src, "src", torch.float32), dp, _code(dst), src.shape[0], src.shape[1], ld, _stream()),
+           "rows_cast")
+
+
+def scale_cap(x, factor: float, cap: float) -> None:
+    """x <- x factor, then cap tanh(x / cap) where cap > 0; float32, in place."""
+    _check(library().ls_scale_cap(_dev(x, "x", torch.float32), x.numel(), float(factor), float(cap), _stream()), "scale_cap")
 
 
 def _rows(t: torch.Tensor, name: str) -> tuple[int, int]:
@@ -455,8 +527,10 @@ def _slopes(slopes, nq: int) -> int:
 
 
 def attention_tile(q, pages, out, part_acc, part_ml, work, n_work, block_table, nq, nkv, d,
-                   window, scale, err, slopes=None, log_rates=None, sinks=None) -> None:
-    """``slopes`` (float32 [nq] or None): slopes[head] x (key position - query position) is added
+                   window, scale, err, slopes=None, log_rates=None, sinks=None, softcap: float = 0.0) -> None:
+    """``window`` > 0: a query reads the last ``window`` positions; < 0: the positions of its own chunk of
+    ``-window`` positions, chunks counted from position 0; 0: every earlier position.  ``softcap`` > 0: the scaled
+    score becomes softcap tanh(score / softcap) before any bias.  ``slopes`` (float32 [nq] or None): slopes[head] x (key position - query position) is added
     to every score; with ``log_rates`` [nq] as well, slopes[head] x ln(1 + log_rates[head] x (query
     position - key position)) is taken off instead.  ``sinks`` [nq]: exp(sinks[head]) is one more
     term of the softmax's denominator (rows that write ``out``; partials get theirs in
@@ -465,20 +539,20 @@ def attention_tile(q, pages, out, part_acc, part_ml, work, n_work, block_table, 
         _dev(q, "q"), _dev(pages, "pages", q.dtype), _opt(out, "out", q.dtype),
         _opt(part_acc, "part_acc", torch.float32), _opt(part_ml, "part_ml", torch.float32), _code(q),
         _dev(work, "work", torch.int32), n_work, _dev(block_table, "block_table", torch.int32),
-        block_table.shape[-1], nq, nkv, d, pages.shape[3], pages.shape[0], int(window), float(scale),
+        block_table.shape[-1], nq, nkv, d, pages.shape[3], pages.shape[0], int(window), float(scale), float(softcap),
         _slopes(slopes, nq), _slopes(log_rates, nq), _slopes(sinks, nq), _dev(err, "err", torch.int32),
         _stream()), "attention_tile")
 
 
 def attention_decode(q, pages, part_acc, part_ml, work, n_work, block_table, nq, nkv, d, window,
-                     scale, err, slopes=None, log_rates=None) -> bool:
+                     scale, err, slopes=None, log_rates=None, softcap: float = 0.0) -> bool:
     """Returns False (and launches nothing) for shapes the decode kernel does not take."""
     status = library().ls_attention_decode(
         _dev(q, "q"), _dev(pages, "pages", q.dtype), _dev(part_acc, "part_acc", torch.float32),
         _dev(part_ml, "part_ml", torch.float32), _code(q), _dev(work, "work", torch.int32), n_work,
         _dev(block_table, "block_table", torch.int32), block_table.shape[-1], nq, nkv, d,
-        pages.shape[3], pages.shape[0], int(window), float(scale), _slopes(slopes, nq), _slopes(log_rates, nq),
-        _dev(err, "err", torch.int32), _stream())
+        pages.shape[3], pages.shape[0], int(window), float(scale), float(softcap), _slopes(slopes, nq),
+        _slopes(log_rates, nq), _dev(err, "err", torch.int32), _stream())
     if status == -2:
         return False
     _check(status, "attention_decode")
@@ -842,8 +916,8 @@ def tanh_rows(x) -> None:
 
 def state_rule(rule: int, dtype, portions, max_portions: int, state, in_a, in_b, in_v, decay, beta, bonus, out,
                carry_src, carry_width: int, carry_rows: int, heads: int, groups: int, dk: int, dv: int,
-               out_scale: float = 1.0) -> None:
-    """Walks every portion of the step through a state rule (RULE_DELTA, RULE_WKV, RULE_GLA), reading and
+               out_scale: float = 1.0, decay_fixed: bool = False) -> None:
+    """(``decay_fixed``: ``decay`` is one row [heads dk] that serves every token.)  Walks every portion of the step through a state rule (RULE_DELTA, RULE_WKV, RULE_GLA), reading and
     writing ``state[slot]`` (float32: the matrix state, then the carried inputs).  RULE_GLA (S <- diag(decay) S
     + k v^T, o = out_scale S^T q) carries nothing else; its ``in_a``, ``in_b``, ``in_v`` (q, k, v in the engine's
     type) may be views of columns of one wider tensor."""
@@ -860,7 +934,7 @@ def state_rule(rule: int, dtype, portions, max_portions: int, state, in_a, in_b,
         _dev(decay, "decay", torch.float32), _opt(beta, "beta", torch.float32), _opt(bonus, "bonus", torch.float32),
         _dev(out, "out", torch.float32), _opt(carry_src, "carry_src", dtype),
         carry_src.shape[1] if carry_src is not None else 0, carry_width,
-        carry_rows, heads, groups, dk, dv, in_ld, float(out_scale), _stream()), "state_rule")
+        carry_rows, heads, groups, dk, dv, in_ld, float(out_scale), 0 if decay_fixed else -1, _stream()), "state_rule")
 
 
 def head_rms_gate(o, gain, gate_f32, gate_x, out, heads: int, dv: int, gain_shared: bool, eps: float,
@@ -877,6 +951,54 @@ def head_rms_gate(o, gain, gate_f32, gate_x, out, heads: int, dv: int, gain_shar
         _dev(o, "o", torch.float32), _dev(gain, "gain", torch.float32), _opt(gate_f32, "gate_f32", torch.float32),
         gate_p, _dev(out, "out"), _code(out), o.shape[0], heads, dv,
         1 if gain_shared else 0, 1 if gate_logit else 0, float(eps), gate_ld, _stream()), "head_rms_gate")
+
+
+def unit_gates(proj, x_at: int, x_bias, conv_w, conv_b, state, token_slot, w_r, w_i, b_r, b_i, rate, a_out, b_out,
+               blocks: int, taps: int, c: float) -> None:
+    """Decays and input terms of a gated recurrent unit per channel (csrc/unit_recurrence.cu): ``proj`` [tokens, *]
+    holds the unit's x projection from column ``x_at`` on; ``w_r``, ``w_i`` [blocks, in, out] in the type of ``proj``."""
+    tokens, width = a_out.shape
+    bw = width // blocks
+    if tuple(w_r.shape) != (blocks, bw, bw) or tuple(w_i.shape) != (blocks, bw, bw) or w_r.dtype != proj.dtype \
+            or b_out.shape != a_out.shape or conv_w.shape != (width, taps) or state.shape[1] < taps * width:
+        raise KernelError("unit_gates: shapes do not agree")
+    pp, ld = _rows(proj, "proj")
+    _check(library("seq").ls_unit_gates(
+        pp, ld, int(x_at), _code(proj), _dev(x_bias, "x_bias", torch.float32), _dev(conv_w, "conv_w", torch.float32),
+        _dev(conv_b, "conv_b", torch.float32), _dev(state, "state", torch.float32), state.stride(0),
+        _dev(token_slot, "token_slot", torch.int32), _dev(w_r, "w_r"), _dev(w_i, "w_i"), _dev(b_r, "b_r", torch.float32),
+        _dev(b_i, "b_i", torch.float32), _dev(rate, "rate", torch.float32), _dev(a_out, "a_out", torch.float32),
+        _dev(b_out, "b_out", torch.float32), tokens, width, int(blocks), int(taps), float(c), _stream()), "unit_gates")
+
+
+def unit_scan(portions, max_portions: int, a, b, proj, y_at: int, x_at: int, y_bias, x_bias, state, out, taps: int) -> None:
+    """S <- a S + b along every portion, out = S gelu(y + bias); the slot keeps S and the convolution's last
+    ``taps`` - 1 inputs (csrc/unit_recurrence.cu)."""
+    tokens, width = a.shape
+    if out.shape != a.shape or out.dtype != proj.dtype or b.shape != a.shape:
+        raise KernelError("unit_scan: shapes do not agree")
+    pp, ld = _rows(proj, "proj")
+    _check(library("seq").ls_unit_scan(
+        _dev(portions, "portions", torch.int32), int(max_portions), _dev(a, "a", torch.float32), _dev(b, "b", torch.float32),
+        pp, ld, int(y_at), int(x_at), _code(proj), _dev(y_bias, "y_bias", torch.float32), _dev(x_bias, "x_bias", torch.float32),
+        _dev(state, "state", torch.float32), state.stride(0), _dev(out, "out"), width, int(taps), _stream()), "unit_scan")
+
+
+def rotate_rows(proj, q_at: int, k_at: int, v_at: int, cos, sin, positions, out, heads: int, dk: int, dv: int, rot_dim: int,
+                k_scale: float, err) -> None:
+    """out [tokens, 2 heads dk + heads dv] float32: the queries and keys of ``proj`` (columns from ``q_at`` / ``k_at``)
+    with the first ``rot_dim`` elements of every head rotated (halves layout), the keys times ``k_scale``, then the values."""
+    tokens = out.shape[0]
+    if out.shape[1] != heads * (2 * dk + dv) or proj.shape[0] != tokens:
+        raise KernelError("rotate_rows: shapes do not agree")
+    if rot_dim and (cos.shape != sin.shape or cos.shape[1] != rot_dim // 2):
+        raise KernelError("rotate_rows: rotary tables do not match rot_dim")
+    pp, ld = _rows(proj, "proj")
+    _check(library("seq").ls_rotate_rows(
+        pp, ld, int(q_at), int(k_at), int(v_at), _code(proj), _opt(cos if rot_dim else None, "cos", torch.float32),
+        _opt(sin if rot_dim else None, "sin", torch.float32), _dev(positions, "positions", torch.int32),
+        _dev(out, "out", torch.float32), tokens, heads, dk, dv, rot_dim, cos.shape[0] if rot_dim else 0, float(k_scale),
+        _dev(err, "err", torch.int32), _stream()), "rotate_rows")
 
 
 def experts_tile_rows(tensor_cores: bool = False) -> int:
@@ -899,7 +1021,7 @@ def experts_route(logits, top: int, ids, weights, experts: int | None = None, so
         raise KernelError("experts_route: logits must be float32")
     lp, l_ld = _rows(logits, "logits")
     _check(library("seq").ls_experts_route(lp, l_ld, tokens, experts, top,
-                                           1 if softmax else 0, _opt(correction, "correction", torch.float32),
+                                           int(softmax), _opt(correction, "correction", torch.float32),
                                            _dev(ids, "ids", torch.int32), _dev(weights, "weights", torch.float32),
                                            _stream()), "experts_route")
 
@@ -944,7 +1066,7 @@ def experts_route_plan(logits, top: int, ids, weights, experts: int, softmax: bo
         raise KernelError("experts_route_plan: the logits or the correction do not match")
     lp, l_ld = _rows(logits, "logits")
     _check(library("seq").ls_experts_route_plan(
-        lp, l_ld, tokens, experts, top, 1 if softmax else 0, _opt(correction, "correction", torch.float32),
+        lp, l_ld, tokens, experts, top, int(softmax), _opt(correction, "correction", torch.float32),
         _dev(ids, "ids", torch.int32), _dev(weights, "weights", torch.float32), real, tile_rows,
         _dev(plan, "plan", torch.int32), max_tiles, _dev(row_token, "row_token", torch.int32),
         _dev(row_weight, "row_weight", torch.float32), _dev(pair_row, "pair_row", torch.int32),

@@ -2,7 +2,7 @@
 
 from .base import (Block, CacheNeed, FeedForward, Mixer, Norm, Part, PositionEncoding, Runtime,
                    WeightSpec, build_part, known_parts, register_part, unregister_part)
-from . import (attention, block, embedding, experts, latent, mlp, norm, parallel, position,  # register the built-in parts
+from . import (attention, block, embedding, experts, injection, latent, mlp, norm, parallel, position,  # register the built-in parts
                recurrent)
 
 __all__ = [

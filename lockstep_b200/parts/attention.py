@@ -24,6 +24,12 @@ Further parameters, for designs that differ from that one:
   1 + c ln(floor((p + 1) / n) + 1).
 - ``score_bias`` "log_distance": r1[head] ln(1 + r2[head] (i - j)) is taken off the score of query i
   with key j; r1 and r2 are tensors of the layer, one number per query head (``names``: ``r1``, ``r2``).
+- ``bias`` "qkv": biases on q, k and v only (none on the output projection).
+- ``value_from_key``: there is no value projection; the values are the keys as projected, before any norm or
+  rotation (the key matrix serves twice in the one product; value heads have the size of key heads).
+- ``chunk``: a query sees the earlier keys of its own chunk of ``chunk`` positions only, chunks counted from
+  position 0 of the sequence (the kernels take it as a negative window; every page is kept).
+- ``softcap``: the scaled score becomes softcap tanh(score / softcap) before any bias is taken off (CUDA-core kernels).
 - ``sink``: a learned number per query head (``names``: ``sink``) whose exponential is one more term
   of the softmax's denominator; it has no key and no value.
 """
@@ -53,11 +59,11 @@ class ScoreExtras:
     tensor-core kernels know the logarithmic bias and sinks; a linear bias keeps the attention on
     the CUDA-core kernels."""
 
-    def __init__(self, slopes=None, log_rates=None, sinks=None):
-        self.slopes, self.log_rates, self.sinks = slopes, log_rates, sinks
+    def __init__(self, slopes=None, log_rates=None, sinks=None, softcap: float = 0.0):
+        self.slopes, self.log_rates, self.sinks, self.softcap = slopes, log_rates, sinks, float(softcap or 0.0)
 
     def tensor_cores(self) -> bool:
-        return self.slopes is None or self.log_rates is not None
+        return (self.slopes is None or self.log_rates is not None) and not self.softcap
 
 
 def attend(rt: Runtime, q, ctx, cache, nq: int, nkv: int, d: int, window: int, scale: float, exact: bool,
@@ -65,7 +71,7 @@ def attend(rt: Runtime, q, ctx, cache, nq: int, nkv: int, d: int, window: int, s
     """Causal attention of the step's queries ``q`` [tokens, nq d] over a layer's pages (heads of one
     size ``d``): prompt portions by tiles, single tokens by splits and a fold.  Returns [tokens, nq d]
     in the engine's type.  ``exact``: every row takes the tile kernel, so that a row's bits do not
-    depend on whether it was decoded or part of a prompt."""
+    depend on whether it was decoded or part of a prompt.  ``window`` < 0: chunks of -window positions."""
     t = q.shape[0]
     tensor_core_attention = not exact and extras.tensor_cores()
     attn = rt.rows(t, nq * d)
@@ -80,7 +86,7 @@ def attend(rt: Runtime, q, ctx, cache, nq: int, nkv: int, d: int, window: int, s
         if plan.n_tile:
             K.attention_tile(q, cache.pages, attn, None, None, plan.tile_work, plan.n_tile,
                              cache.block_table, nq, nkv, d, window, scale, rt.err, extras.slopes,
-                             extras.log_rates, extras.sinks)
+                             extras.log_rates, extras.sinks, softcap=extras.softcap)
     if plan.n_split:
         part_acc = rt.rows(plan.n_slots, nq, d, dtype=torch.float32)
         part_ml = rt.rows(plan.n_slots, nq, 2, dtype=torch.float32)
@@ -92,11 +98,11 @@ def attend(rt: Runtime, q, ctx, cache, nq: int, nkv: int, d: int, window: int, s
         if not done and not exact:
             done = K.attention_decode(q, cache.pages, part_acc, part_ml, plan.split_work,
                                       plan.n_split, cache.block_table, nq, nkv, d, window,
-                                      scale, rt.err, extras.slopes, extras.log_rates)
+                                      scale, rt.err, extras.slopes, extras.log_rates, softcap=extras.softcap)
         if not done:
             K.attention_tile(q, cache.pages, None, part_acc, part_ml, plan.split_work,
                              plan.n_split, cache.block_table, nq, nkv, d, window,
-                             scale, rt.err, extras.slopes, extras.log_rates)
+                             scale, rt.err, extras.slopes, extras.log_rates, softcap=extras.softcap)
         K.attention_combine(part_acc, part_ml, attn, plan.combine_items, plan.n_combine, nq, d, extras.sinks)
     return attn
 
@@ -108,7 +114,8 @@ class GQAttention(Mixer):
 
     def __init__(self, hidden_size, num_heads, num_kv_heads, head_dim, scale, window, qk_norm_eps,
                  position: PositionEncoding, runtime: Runtime, value_dim=None, qk_norm_scope="head",
-                 borrows_kv=False, names=None, bias=False, q_temp=None, score_bias=None, sink=False):
+                 borrows_kv=False, names=None, bias=False, q_temp=None, score_bias=None, sink=False,
+                 value_from_key=False, chunk=0, softcap=0.0):
         if num_heads % num_kv_heads:
             raise ValueError("num_heads must be a multiple of num_kv_heads")
         if qk_norm_scope not in ("head", "projection"):
@@ -119,6 +126,12 @@ class GQAttention(Mixer):
         if score_bias not in (None, "log_distance"):
             raise ValueError(f"score_bias must be log_distance or absent, got {score_bias!r}")
         self.bias, self.score_bias, self.sink = bool(bias), score_bias, bool(sink)
+        self.output_biased = bool(bias) and bias != "qkv"
+        self.value_from_key, self.chunk, self.softcap = bool(value_from_key), int(chunk or 0), float(softcap or 0.0)
+        if self.value_from_key and (self.dv != self.d or self.borrows or self.bias):
+            raise ValueError("value_from_key: value heads have the size of key heads, and the layer projects its own keys without biases")
+        if self.chunk < 0 or (self.chunk and window):
+            raise ValueError("chunk must be positive, and a layer has a window or chunks, not both")
         self.q_temp = (float(q_temp["coef"]), int(q_temp["every"])) if q_temp else None
         if self.q_temp is not None and self.q_temp[1] <= 0:
             raise ValueError("q_temp.every must be positive")
@@ -134,6 +147,7 @@ class GQAttention(Mixer):
         self.names = dict(_DEFAULT_NAMES)
         self.names.update(names or {})
         self.scale, self.window = float(scale), int(window or 0)
+        self.mask = -self.chunk if self.chunk else self.window     # what the attention kernels and plans are given
         self.qk_norm_eps = qk_norm_eps
         self.position, self.rt = position, runtime
         self.w_qkv = self.w_o = self.q_gain = self.k_gain = self.qkv_bias = self.o_bias = None
@@ -146,7 +160,7 @@ class GQAttention(Mixer):
         return CacheNeed("paged_kv", kv_heads=self.nkv, head_dim=self.pad, window=self.window)
 
     def attention_windows(self):
-        return {self.window}
+        return {self.mask}
 
     def weight_specs(self):
         n = self.names
@@ -155,7 +169,8 @@ class GQAttention(Mixer):
                  n["o"]: WeightSpec((self.h, self.nq * self.dv))}
         if not self.borrows:
             specs[n["k"]] = WeightSpec((self.nkv * self.d, self.h))
-            specs[n["v"]] = WeightSpec((self.nkv * self.dv, self.h))
+            if not self.value_from_key:
+                specs[n["v"]] = WeightSpec((self.nkv * self.dv, self.h))
         if self.qk_norm_eps is not None:
             specs[n["q_norm"]] = WeightSpec((self.nq * self.d if whole else self.d,), "gain")
             if not self.borrows:
@@ -163,7 +178,8 @@ class GQAttention(Mixer):
         small = ("normal", 0.0, 0.02)
         if self.bias:
             specs[n["q_bias"]] = WeightSpec((self.nq * self.d,), "gain", small)
-            specs[n["o_bias"]] = WeightSpec((self.h,), "gain", small)
+            if self.output_biased:
+                specs[n["o_bias"]] = WeightSpec((self.h,), "gain", small)
             if not self.borrows:
                 specs[n["k_bias"]] = WeightSpec((self.nkv * self.d,), "gain", small)
                 specs[n["v_bias"]] = WeightSpec((self.nkv * self.dv,), "gain", small)
@@ -176,7 +192,8 @@ class GQAttention(Mixer):
 
     def bind(self, tensors):
         n = self.names
-        parts = [tensors[n["q"]]] if self.borrows else [tensors[n["q"]], tensors[n["k"]], tensors[n["v"]]]
+        parts = [tensors[n["q"]]] if self.borrows else \
+            [tensors[n["q"]], tensors[n["k"]], tensors[n["k" if self.value_from_key else "v"]]]
         self.w_qkv = torch.cat(parts, dim=0).contiguous()
         self.w_o = tensors[n["o"]]
         if self.pad != self.dv:
@@ -192,10 +209,11 @@ class GQAttention(Mixer):
             self.extras = ScoreExtras(slopes=_f32(tensors[n["r1"]]), log_rates=_f32(tensors[n["r2"]]))
         if self.sink:
             self.extras.sinks = _f32(tensors[n["sink"]])
+        self.extras.softcap = self.softcap
         if self.bias:
             parts = [tensors[n["q_bias"]]] if self.borrows else [tensors[n[k]] for k in ("q_bias", "k_bias", "v_bias")]
             self.qkv_bias = _f32(torch.cat([p.reshape(-1) for p in parts]))
-            self.o_bias = _f32(tensors[n["o_bias"]])
+            self.o_bias = _f32(tensors[n["o_bias"]]) if self.output_biased else None
         if self.qk_norm_eps is not None:
             self.q_gain = tensors[n["q_norm"]]
             self.k_gain = None if self.borrows else tensors[n["k_norm"]]
@@ -250,7 +268,7 @@ class GQAttention(Mixer):
         self._attend(q, ctx, cache, residual, t, overwrite)
 
     def _attend(self, q, ctx, cache, residual, t, overwrite=False):
-        attn = attend(self.rt, q, ctx, cache, self.nq, self.nkv, self.pad, self.window, self.scale, self.exact,
+        attn = attend(self.rt, q, ctx, cache, self.nq, self.nkv, self.pad, self.mask, self.scale, self.exact,
                       self.extras)
         if overwrite:
             K.gemm_nt(attn, self.w_o, residual, K.EPILOGUE_STORE, err=self.rt.err)
@@ -267,4 +285,5 @@ def _build(spec, runtime, position=None, **_):
                        value_dim=spec.get("value_dim"), qk_norm_scope=spec.get("qk_norm_scope", "head"),
                        borrows_kv=spec.get("borrows_kv", False), names=spec.get("names"),
                        bias=spec.get("bias", False), q_temp=spec.get("q_temp"), score_bias=spec.get("score_bias"),
-                       sink=spec.get("sink", False))
+                       sink=spec.get("sink", False), value_from_key=spec.get("value_from_key", False),
+                       chunk=spec.get("chunk", 0), softcap=spec.get("softcap", 0.0))

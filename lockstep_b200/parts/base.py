@@ -184,6 +184,9 @@ class Mixer(Part):
     # mixer stores its result there instead of adding it, without its output projection's bias, which the caller
     # gets from ``output_bias()`` and adds itself (mixers side by side: one kernel weights and adds them all).
     can_overwrite = False
+    # True for a mixer whose ``forward`` takes ``post_norm`` (a layer norm with ``gain`` and ``eps``): the mixer then
+    # adds post_norm(its result) to ``residual`` in its own closing kernel
+    accepts_post_norm = False
 
     def cache_need(self) -> CacheNeed | None:
         return None
@@ -228,7 +231,7 @@ class Block(Part):
 # registries: (category, kind) -> builder(spec, runtime, **extra) -> Part
 # ---------------------------------------------------------------------------
 
-CATEGORIES = ("block", "mixer", "feed_forward", "norm", "position", "embedding", "head")
+CATEGORIES = ("block", "mixer", "feed_forward", "norm", "position", "embedding", "head", "injection")
 _BUILDERS: dict[tuple[str, str], Callable[..., Part]] = {}
 
 

@@ -4,6 +4,12 @@ The names under which the layer's tensors are stored are parameters of the
 arrangement, so the same arrangement serves architectures that name them otherwise.
 A layer whose feed-forward is of kind "none" is its mixer alone.
 
+"sandwich_norm": a norm after each sublayer as well as before it,
+h += norm_c(mixer(norm_a(h))); h += norm_d(feed_forward(norm_b(h))).  The norms after the sublayers are the
+``LayerSpec.extra`` parts "mixer_post_norm" and "feed_forward_post_norm" (norms with ``accumulate``); a sublayer
+stores its result in a float32 buffer and the norm's kernel adds the normed rows to the stream, or, where the
+mixer closes with a kernel of its own that can take the norm along (``Mixer.accepts_post_norm``), that kernel does.
+
 "shared_norm": one norm feeds the mixer and the feed-forward side by side,
 h += mixer(y) + feed_forward(y) with y = norm(h).  Two options, each with tensors of the layer:
 - ``shift``: the mixer reads y_t + (y_(t-1) - y_t) * mix instead of y_t (``mix`` one number per
@@ -97,6 +103,50 @@ class PreNormBlock(Block):
 @register_part("block", "pre_norm")
 def _build(spec, runtime, layer_spec=None, **_):
     return PreNormBlock(layer_spec, runtime)
+
+
+class SandwichNormBlock(PreNormBlock):
+    def __init__(self, layer_spec, runtime: Runtime):
+        super().__init__(layer_spec, runtime)
+        self.rt = runtime
+        self.names.setdefault("mixer_post_norm", "post_attention_norm")
+        self.names.setdefault("feed_forward_post_norm", "post_mlp_norm")
+        self.mixer_post_norm = build_part("norm", layer_spec.extra["mixer_post_norm"], runtime)
+        self.feed_forward_post_norm = None
+        if self.feed_forward is not None:
+            self.feed_forward_post_norm = build_part("norm", layer_spec.extra["feed_forward_post_norm"], runtime)
+        for post in (self.mixer_post_norm, self.feed_forward_post_norm):
+            if post is not None and not hasattr(post, "accumulate"):
+                raise ValueError("sandwich_norm: the norm after a sublayer must be able to add its result to the stream")
+
+    def _children(self):
+        keys = list(_DEFAULT_NAMES) + ["mixer_post_norm", "feed_forward_post_norm"]
+        return [(self.names[k], getattr(self, k)) for k in keys if getattr(self, k) is not None]
+
+    def _sublayer(self, part, post, x, h, ctx, cache=None):
+        args = (x, ctx, cache) if cache is not None else (x, ctx)
+        if getattr(part, "accepts_post_norm", False):
+            part.forward(*args, h, post_norm=post)
+            return
+        out = self.rt.rows(h.shape[0], h.shape[1], dtype=torch.float32)
+        if part.can_overwrite:
+            part.forward(*args, out, overwrite=True)
+        else:
+            K.row_bias(out, None)
+            part.forward(*args, out)
+        post.accumulate(h, out)
+
+    def _mix(self, h, ctx, cache):
+        self._sublayer(self.mixer, self.mixer_post_norm, self._normed(self.mixer_norm, self.mixer, h), h, ctx, cache)
+
+    def _feed_forward(self, h, ctx, cache):
+        self._sublayer(self.feed_forward, self.feed_forward_post_norm,
+                       self._normed(self.feed_forward_norm, self.feed_forward, h), h, ctx)
+
+
+@register_part("block", "sandwich_norm")
+def _build_sandwich(spec, runtime, layer_spec=None, **_):
+    return SandwichNormBlock(layer_spec, runtime)
 
 
 _SHARED_NAMES = {"norm": "norm", "mixer": "mixer", "feed_forward": "mlp", "shift": "shift",

@@ -1,12 +1,12 @@
 """A feed-forward of routed experts.
 
 Router logits z = W_router x in float32; scores from ``score`` of z ("sigmoid", or "softmax" over all
-experts); the ``top`` largest scores chosen (ties to the lower index), with ``correction`` after
+experts, or "softmax_chosen": the logits themselves, and the weights the softmax over the chosen logits alone); the ``top`` largest scores chosen (ties to the lower index), with ``correction`` after
 adding a stored number per expert that only the choice sees; the weight of a chosen expert is its
 score (not renormalised).  ``scale`` "input": the weight multiplies what goes into the expert;
 "output": what comes out of it.  An expert is down(act(up(.))) without biases, with ``activation``
 "relu2" (the square of relu) or "clamped_glu" (gate and up maps, g = min(gate, limit), u =
-clamp(up, -limit, limit), g sigmoid(alpha g) (u + 1)).  The last ``identity`` of the router's
+clamp(up, -limit, limit), g sigmoid(alpha g) (u + 1)) or "swiglu" (silu(gate) up, no clamps).  The last ``identity`` of the router's
 outputs are experts without tensors that return their input.  ``shared`` = {"ff", "limit", "gate"}:
 one more expert of the same form that every token runs, added with the weight sigmoid(w_g . x)
 where ``gate`` is set (else one).  The token's chosen experts are summed in order of rank, the
@@ -37,14 +37,20 @@ class RoutedExperts(FeedForward):
     def __init__(self, hidden_size: int, expert_size: int, experts: int, top: int, runtime: Runtime,
                  score: str = "sigmoid", activation: str = "relu2", scale: str = "input", limit: float = 0.0,
                  alpha: float = 1.702, identity: int = 0, correction: bool = False, shared=None, names=None):
-        if score not in ("sigmoid", "softmax") or activation not in ("relu2", "clamped_glu") or scale not in ("input", "output"):
+        if score not in ("sigmoid", "softmax", "softmax_chosen") or activation not in ("relu2", "clamped_glu", "swiglu") \
+                or scale not in ("input", "output"):
             raise ValueError(f"routed_experts: score {score!r}, activation {activation!r} or scale {scale!r} is not known")
         if experts < 1 or identity < 0 or not 1 <= top <= experts + identity or experts + identity > 512:
             raise ValueError(f"top {top} of {experts} + {identity} experts is not supported (up to 512 experts)")
         self.h, self.f, self.E, self.top, self.rt = int(hidden_size), int(expert_size), int(experts), int(top), runtime
         self.score, self.activation, self.scale = score, activation, scale
         self.limit, self.alpha, self.identity, self.correction = float(limit), float(alpha), int(identity), bool(correction)
-        self.glu = activation == "clamped_glu"
+        self.glu = activation in ("clamped_glu", "swiglu")
+        # "swiglu" is the gated unit without clamps, with the sigmoid's slope 1 and nothing added to u
+        self.up_offset = 1.0
+        if activation == "swiglu":
+            self.limit, self.alpha, self.up_offset = 0.0, 1.0, 0.0
+        self.score_mode = {"sigmoid": 0, "softmax": 1, "softmax_chosen": 2}[score]
         if shared and not self.glu:
             raise ValueError("routed_experts: a shared expert takes the gated activation (clamped_glu)")
         self.shared = dict(shared) if shared else None
@@ -100,7 +106,7 @@ class RoutedExperts(FeedForward):
 
     def _activate(self, wide, rows, f):
         act = self.rt.rows(rows, f)
-        K.clamped_glu(wide, None, act, self.limit if self.limit > 0 else float("inf"), self.alpha)
+        K.clamped_glu(wide, None, act, self.limit if self.limit > 0 else float("inf"), self.alpha, up_offset=self.up_offset)
         return act
 
     def _shared(self, first, tokens):
@@ -109,7 +115,7 @@ class RoutedExperts(FeedForward):
         wide = first[:, self.shared_at:self.shared_at + 2 * f]
         act = rt.rows(tokens, f)
         limit = float(self.shared.get("limit", self.limit))
-        K.clamped_glu(wide, None, act, limit if limit > 0 else float("inf"), self.alpha)
+        K.clamped_glu(wide, None, act, limit if limit > 0 else float("inf"), self.alpha, up_offset=self.up_offset)
         out = rt.rows(tokens, self.h, dtype=torch.float32)
         K.gemm_nt(act, self.w_shared_down, out, err=rt.err)
         return out
@@ -141,10 +147,10 @@ class RoutedExperts(FeedForward):
         pair_row = rt.rows(pairs, dtype=i32)
         if tokens <= K.FEW_TOKENS:
             # few tokens: the choice and the plan in one launch of one block
-            K.experts_route_plan(logits, self.top, ids, weights, routed, self.score == "softmax", self.bias, self.E, tile,
+            K.experts_route_plan(logits, self.top, ids, weights, routed, self.score_mode, self.bias, self.E, tile,
                                  plan, max_tiles, row_token, row_weight, pair_row, rt.err)
         else:
-            K.experts_route(logits, self.top, ids, weights, experts=routed, softmax=self.score == "softmax",
+            K.experts_route(logits, self.top, ids, weights, experts=routed, softmax=self.score_mode,
                             correction=self.bias)
             K.experts_plan(ids, weights, self.E, tile, plan, max_tiles, row_token, row_weight, pair_row, rt.err)
         on_input = self.scale == "input"

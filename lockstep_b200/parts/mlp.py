@@ -88,6 +88,50 @@ class ClampedGLU(FeedForward):
         K.gemm_nt(act, self.w_down, residual, K.EPILOGUE_RESIDUAL, err=self.rt.err)
 
 
+class GatedUnit(FeedForward):
+    """down(act(gate(x)) * up(x)) without biases, ``activation`` "gelu_tanh" (0.5 z (1 + tanh(sqrt(2 / pi) (z +
+    0.044715 z^3)))) or "silu".  gate and up are one product with a float32 result, the activation a kernel."""
+
+    graph_safe = True
+    accepts_normed_rows = True
+    can_overwrite = True
+
+    def __init__(self, hidden_size: int, intermediate_size: int, activation: str, runtime: Runtime, names=None):
+        if activation not in ("gelu_tanh", "silu"):
+            raise ValueError(f"gated_unit: activation {activation!r} is not known (gelu_tanh, silu)")
+        self.h, self.i, self.activation, self.rt = int(hidden_size), int(intermediate_size), activation, runtime
+        self.names = {"gate": "gate", "up": "up", "down": "down"}
+        self.names.update(names or {})
+        self.w_gate_up = self.w_down = None
+
+    def weight_specs(self):
+        n = self.names
+        return {n["gate"]: WeightSpec((self.i, self.h)), n["up"]: WeightSpec((self.i, self.h)),
+                n["down"]: WeightSpec((self.h, self.i))}
+
+    def bind(self, tensors):
+        n = self.names
+        self.w_gate_up = torch.cat([tensors[n["gate"]], tensors[n["up"]]], dim=0).contiguous()
+        self.w_down = tensors[n["down"]]
+
+    def forward(self, x, ctx, residual, overwrite=False):
+        rows = residual.shape[0]
+        gate_up = self.rt.rows(rows, 2 * self.i, dtype=torch.float32)
+        if isinstance(x, NormedRows):
+            x.linear(self.w_gate_up, gate_up, K.EPILOGUE_STORE, self.rt.err)
+        else:
+            K.gemm_nt(x, self.w_gate_up, gate_up, K.EPILOGUE_STORE, err=self.rt.err)
+        act = self.rt.rows(rows, self.i)
+        K.clamped_glu(gate_up, None, act, float("inf"), 1.0, up_offset=0.0, gelu=self.activation == "gelu_tanh")
+        K.gemm_nt(act, self.w_down, residual, K.EPILOGUE_STORE if overwrite else K.EPILOGUE_RESIDUAL, err=self.rt.err)
+
+
+@register_part("feed_forward", "gated_unit")
+def _build_gated_unit(spec, runtime, **_):
+    return GatedUnit(spec["hidden_size"], spec["intermediate_size"], spec.get("activation", "gelu_tanh"), runtime,
+                     names=spec.get("names"))
+
+
 @register_part("feed_forward", "clamped_glu")
 def _build_clamped_glu(spec, runtime, **_):
     return ClampedGLU(spec["hidden_size"], spec["intermediate_size"], spec["limit"], spec.get("alpha", 1.702),

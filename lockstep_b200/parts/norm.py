@@ -4,7 +4,11 @@ this number (a tensor that holds the gain minus one: offset 1); the sum is made 
 weights arrive.  ``tensor``: the local name of the stored tensor ("weight"; "" where the norm's
 own prefix names it).  ``groups`` > 1: the row is cut into that many equal consecutive parts and
 each is divided by its own root mean square (the gain still runs over the whole row).  ``scalar``:
-the stored gain is one number for all coordinates (a tensor without dimensions)."""
+the stored gain is one number for all coordinates (a tensor without dimensions).
+
+"layernorm": y = (x - mean) * rsqrt(var + eps) * gain with var the mean of the squared deviations and no bias,
+all in float32.  ``accumulate(residual, x)`` adds the norm of float32 rows ``x`` to ``residual`` (a norm that
+follows a sublayer)."""
 
 from __future__ import annotations
 
@@ -79,3 +83,32 @@ class RMSNorm(Norm):
 def _build(spec, runtime, **_):
     return RMSNorm(spec["width"], spec["eps"], runtime, spec.get("offset", 0.0), spec.get("tensor", "weight"),
                    spec.get("groups", 1), spec.get("scalar", False))
+
+
+class LayerNorm(Norm):
+    graph_safe = True
+
+    def __init__(self, width: int, eps: float, runtime: Runtime, tensor: str = "weight"):
+        self.width, self.eps, self.rt, self.tensor = int(width), float(eps), runtime, str(tensor)
+        self.gain: torch.Tensor | None = None
+
+    def weight_specs(self):
+        return {self.tensor: WeightSpec((self.width,), "gain")}
+
+    def bind(self, tensors):
+        self.gain = tensors[self.tensor].to(torch.float32).contiguous()
+
+    def forward(self, h, row_index=None):
+        rows = h.shape[0] if row_index is None else row_index.numel()
+        out = self.rt.rows(rows, self.width)
+        K.layernorm(h, self.gain, out, self.eps, self.rt.err, row_index)
+        return out
+
+    def accumulate(self, residual, x):
+        """residual += norm(x); both float32 [rows, width]."""
+        K.norm_merge_add(residual, x.view(1, *x.shape), None, 1.0, self.gain, 0.0, self.eps)
+
+
+@register_part("norm", "layernorm")
+def _build_layernorm(spec, runtime, **_):
+    return LayerNorm(spec["width"], spec["eps"], runtime, spec.get("tensor", "weight"))

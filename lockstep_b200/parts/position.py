@@ -10,6 +10,8 @@ lo = max(floor(dim(fast)), 0), hi = min(ceil(dim(slow)), dim - 1), ramp_i = clam
 0.001), 0, 1), the frequency is f_i / factor * ramp_i + f_i (1 - ramp_i), and cosines and sines are
 multiplied by 0.1 ln(factor) + 1.  Without ``scaling`` it is the plain rotation.  ``interleaved``: a
 pair is elements (2i, 2i + 1) instead of (i, i + dim / 2).
+"distance_slopes": no rotation; the score of a query with a key loses slope_h x their distance, slope_h =
+2^(-``exponent`` (h + 1) / heads) for head h (``exponent`` 8 unless given).  ``dim``, ``theta``: a rotation besides.
 "none": no position encoding.
 """
 
@@ -72,6 +74,21 @@ class ScaledRotary(PositionEncoding):
         return self.cos, self.sin, self.dim
 
 
+class DistanceSlopes(PositionEncoding):
+    graph_safe = True
+
+    def __init__(self, runtime: Runtime, exponent: float = 8.0, dim: int = 0, theta: float = 10000.0):
+        self.exponent, self.rt = float(exponent), runtime
+        self.inner = Rotary(dim, theta, runtime) if dim else None
+
+    def rotary(self):
+        return self.inner.rotary() if self.inner is not None else None
+
+    def score_slopes(self, num_heads: int):
+        s = [2.0 ** (-self.exponent * (h + 1) / num_heads) for h in range(num_heads)]
+        return torch.tensor(s, dtype=torch.float64).to(torch.float32).to(self.rt.device).contiguous()
+
+
 class NoPosition(PositionEncoding):
     graph_safe = True
 
@@ -85,6 +102,11 @@ def _build_rotary(spec, runtime, **_):
 def _build_scaled_rotary(spec, runtime, **_):
     return ScaledRotary(spec["dim"], spec["theta"], runtime, scaling=spec.get("scaling"),
                         interleaved=spec.get("interleaved", False))
+
+
+@register_part("position", "distance_slopes")
+def _build_slopes(spec, runtime, **_):
+    return DistanceSlopes(runtime, spec.get("exponent", 8.0), spec.get("dim", 0), spec.get("theta", 10000.0))
 
 
 @register_part("position", "none")

@@ -23,6 +23,16 @@ output projection.  The slot also carries what the next portion needs of the tok
   made through its logarithm; the read-out is normed per head, times a gain shared by the heads,
   times silu(W_g x).  Nothing but S is carried.
 
+"gated_recurrent_unit" (per channel of ``width`` channels, in ``blocks`` equal parts):
+    u = conv(W_x x + b_x);  r = sigmoid(A_b u_b + a_b), i = sigmoid(I_b u_b + i_b) with square matrices per part;
+    log a = -``rate`` r softplus(lam);  S <- a S + sqrt(1 - a^2) i u;  out = W_o (S gelu(W_y x + b_y))
+  a causal convolution of ``conv_taps`` taps per channel (its last taps - 1 inputs are carried beside S).
+
+"retention" (per head, with one fixed decay per head, ``decay``):
+    S <- decay_h S + k_t v_t^T;  o_t = S^T q_t
+  q and k rotated by the position encoding (k then times dk^(-1/2)); the read-out is divided by its root mean
+  square per head (no gain), times silu(W_g x).  Nothing but S is carried.
+
 The projections run as the engine's products (tensor cores in bfloat16); everything between
 them and the recurrence, the recurrence and the state are float32 (csrc/recurrent.cu).
 """
@@ -252,6 +262,140 @@ class GatedLinear(Mixer):
         y = rt.rows(tokens, self.Vd)
         K.head_rms_gate(o, self.gain, None, proj[:, at["g"]:at["g"] + self.Vd], y, self.H, self.dv, True, self.eps)
         K.gemm_nt(y, self.w_o, residual, K.EPILOGUE_STORE if overwrite else K.EPILOGUE_RESIDUAL, err=rt.err)
+
+
+class GatedRecurrentUnit(Mixer):
+    graph_safe = True
+    accepts_normed_rows = True
+    can_overwrite = True
+
+    def __init__(self, hidden_size, width, blocks, conv_taps, runtime: Runtime, rate: float = 8.0, names=None):
+        if width % blocks:
+            raise ValueError(f"gated_recurrent_unit: {blocks} parts do not divide {width} channels")
+        if not 1 <= conv_taps <= 8:
+            raise ValueError(f"a convolution of {conv_taps} taps is not supported (1 to 8)")
+        self.w, self.C, self.blocks, self.taps = int(hidden_size), int(width), int(blocks), int(conv_taps)
+        self.rate, self.rt = float(rate), runtime
+        self.names = {"y": "y", "y_bias": "y.b", "x": "x", "x_bias": "x.b", "conv": "conv", "conv_bias": "conv.b",
+                      "r": "ra", "r_bias": "ra.b", "i": "ri", "i_bias": "ri.b", "lam": "lam", "o": "o"}
+        self.names.update(names or {})
+
+    def cache_need(self):
+        return CacheNeed("state", state_shape=(self.taps * self.C,), state_dtype=torch.float32)
+
+    def weight_specs(self):
+        n, C, bw = self.names, self.C, self.C // self.blocks
+        small = ("normal", 0.0, 0.02)
+        gate = ("normal", 0.0, bw ** -0.5)
+        return {n["y"]: WeightSpec((C, self.w)), n["y_bias"]: WeightSpec((C,), "gain", small),
+                n["x"]: WeightSpec((C, self.w)), n["x_bias"]: WeightSpec((C,), "gain", small),
+                n["conv"]: WeightSpec((C, self.taps), "gain", ("normal", 0.0, 0.5)),
+                n["conv_bias"]: WeightSpec((C,), "gain", small),
+                n["r"]: WeightSpec((self.blocks, bw, bw), "matrix", gate), n["r_bias"]: WeightSpec((self.blocks, bw), "gain", small),
+                n["i"]: WeightSpec((self.blocks, bw, bw), "matrix", gate), n["i_bias"]: WeightSpec((self.blocks, bw), "gain", small),
+                n["lam"]: WeightSpec((C,), "gain", ("normal", -2.0, 1.0)), n["o"]: WeightSpec((self.w, C))}
+
+    def bind(self, t):
+        n = self.names
+        # one product for both branches: y's columns, then x's from a column that is a multiple of 8
+        pad = -self.C % 8
+        zeros = torch.zeros((pad, self.w), dtype=t[n["y"]].dtype, device=t[n["y"]].device)
+        self.x_at = self.C + pad
+        self.w_in = torch.cat([t[n["y"]], zeros, t[n["x"]]], dim=0).contiguous()
+        self.y_bias, self.x_bias = _f32(t[n["y_bias"]]), _f32(t[n["x_bias"]])
+        self.conv_w, self.conv_b = _f32(t[n["conv"]]), _f32(t[n["conv_bias"]])
+        # the gates' matrices transposed to [part, in, out]: a thread of the gates' kernel owns an output channel
+        self.w_r = t[n["r"]].transpose(1, 2).contiguous()
+        self.w_i = t[n["i"]].transpose(1, 2).contiguous()
+        self.b_r, self.b_i = _f32(t[n["r_bias"]].reshape(-1)), _f32(t[n["i_bias"]].reshape(-1))
+        self.softplus_lam = torch.nn.functional.softplus(_f32(t[n["lam"]])).contiguous()
+        self.w_o = t[n["o"]]
+
+    def forward(self, x, ctx, cache, residual, overwrite=False):
+        rt, tokens = self.rt, residual.shape[0]
+        proj = rt.rows(tokens, self.w_in.shape[0])
+        if isinstance(x, NormedRows):
+            x.linear(self.w_in, proj, K.EPILOGUE_STORE, rt.err)
+        else:
+            K.gemm_nt(x, self.w_in, proj, err=rt.err)
+        a = rt.rows(tokens, self.C, dtype=torch.float32)
+        b = rt.rows(tokens, self.C, dtype=torch.float32)
+        K.unit_gates(proj, self.x_at, self.x_bias, self.conv_w, self.conv_b, cache.state, ctx.token_slot, self.w_r, self.w_i,
+                     self.b_r, self.b_i, self.softplus_lam, a, b, self.blocks, self.taps, self.rate)
+        portions, cap = portion_list(ctx, cache.state, rt)
+        y = rt.rows(tokens, self.C)
+        K.unit_scan(portions, cap, a, b, proj, 0, self.x_at, self.y_bias, self.x_bias, cache.state, y, self.taps)
+        K.gemm_nt(y, self.w_o, residual, K.EPILOGUE_STORE if overwrite else K.EPILOGUE_RESIDUAL, err=rt.err)
+
+
+class Retention(Mixer):
+    graph_safe = True
+    accepts_normed_rows = True
+    can_overwrite = True
+
+    def __init__(self, hidden_size, num_heads, key_dim, value_dim, decay, norm_eps, position, runtime: Runtime):
+        if key_dim > 512:
+            raise ValueError(f"key_dim {key_dim} is not supported (up to 512)")
+        if len(decay) != num_heads or not all(0.0 < float(d) <= 1.0 for d in decay):
+            raise ValueError("retention: one decay in (0, 1] per head")
+        self.w, self.H, self.dk, self.dv = int(hidden_size), int(num_heads), int(key_dim), int(value_dim)
+        self.decay_values, self.eps, self.position, self.rt = [float(d) for d in decay], float(norm_eps), position, runtime
+        self.Kd, self.Vd = self.H * self.dk, self.H * self.dv
+
+    def cache_need(self):
+        return CacheNeed("state", state_shape=(self.H * self.dk * self.dv,), state_dtype=torch.float32)
+
+    def weight_specs(self):
+        return {"q": WeightSpec((self.Kd, self.w)), "k": WeightSpec((self.Kd, self.w)), "v": WeightSpec((self.Vd, self.w)),
+                "g": WeightSpec((self.Vd, self.w)), "o": WeightSpec((self.w, self.Vd))}
+
+    def bind(self, t):
+        zeros = lambda rows: torch.zeros((rows, self.w), dtype=t["q"].dtype, device=t["q"].device)
+        parts, self.at, col = [], {}, 0
+        for name in ("q", "k", "v", "g"):
+            self.at[name] = col
+            parts += [t[name], zeros(-t[name].shape[0] % 8)]
+            col += t[name].shape[0] + (-t[name].shape[0] % 8)
+        self.w_in = torch.cat(parts, dim=0).contiguous()
+        self.w_o = t["o"]
+        dev = t["q"].device
+        self.decay = torch.tensor(self.decay_values, dtype=torch.float32).repeat_interleave(self.dk).to(dev).contiguous()
+        self.ones = torch.ones(self.dv, dtype=torch.float32, device=dev)
+
+    def forward(self, x, ctx, cache, residual, overwrite=False):
+        rt, tokens, at = self.rt, residual.shape[0], self.at
+        proj = rt.rows(tokens, self.w_in.shape[0])
+        if isinstance(x, NormedRows):
+            x.linear(self.w_in, proj, K.EPILOGUE_STORE, rt.err)
+        else:
+            K.gemm_nt(x, self.w_in, proj, err=rt.err)
+        rot = self.position.rotary()
+        cos, sin, rot_dim = rot if rot is not None else (None, None, 0)
+        if rot_dim and self.position.rotary_interleaved:
+            raise ValueError("retention rotates halves of a head")
+        qkv = rt.rows(tokens, 2 * self.Kd + self.Vd, dtype=torch.float32)
+        K.rotate_rows(proj, at["q"], at["k"], at["v"], cos, sin, ctx.positions, qkv, self.H, self.dk, self.dv, rot_dim,
+                      self.dk ** -0.5, rt.err)
+        portions, cap = portion_list(ctx, cache.state, rt)
+        o = rt.rows(tokens, self.Vd, dtype=torch.float32)
+        K.state_rule(K.RULE_GLA, torch.float32, portions, cap, cache.state, qkv[:, :self.Kd], qkv[:, self.Kd:2 * self.Kd],
+                     qkv[:, 2 * self.Kd:], self.decay, None, None, o, None, 0, 0, self.H, self.H, self.dk, self.dv,
+                     decay_fixed=True)
+        y = rt.rows(tokens, self.Vd)
+        K.head_rms_gate(o, self.ones, None, proj[:, at["g"]:at["g"] + self.Vd], y, self.H, self.dv, True, self.eps)
+        K.gemm_nt(y, self.w_o, residual, K.EPILOGUE_STORE if overwrite else K.EPILOGUE_RESIDUAL, err=rt.err)
+
+
+@register_part("mixer", "gated_recurrent_unit")
+def _build_unit(spec, runtime, **_):
+    return GatedRecurrentUnit(spec["hidden_size"], spec["width"], spec["blocks"], spec["conv_taps"], runtime,
+                              rate=spec.get("rate", 8.0), names=spec.get("names"))
+
+
+@register_part("mixer", "retention")
+def _build_retention(spec, runtime, position=None, **_):
+    return Retention(spec["hidden_size"], spec["num_heads"], spec["key_dim"], spec["value_dim"], spec["decay"],
+                     spec["norm_eps"], position, runtime)
 
 
 @register_part("mixer", "gated_linear")
