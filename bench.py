@@ -37,6 +37,7 @@ of an unrecorded step of each with its fraction of the measured peaks.
 bias beside gated linear attention, attention over a cached latent, a clamped gated feed-forward,
 two of the layers run twice) beside Qwen3 layers of equal width, depth, head counts and
 feed-forward size.
+``--workload pikurax`` does the same for the Pikurax design beside Malazen.
 ``--workload kemirax`` does the same for the Kemirax design (one norm feeding a mixer behind a token
 shift and routed experts side by side, gates on both; attention over a cached latent with queries
 through a latent and layers that read another layer's cache; gated linear attention; identity and
@@ -574,7 +575,8 @@ def kernel_times(runner, entries_of, steps=3):
              "attention_prefill_tc", "attention_combine", "qkv_finish", "find_portions", "delta_prep", "shift_mix",
              "tanh_rows", "double_exp_decay", "state_rule", "head_rms_gate", "experts_route", "experts_plan", "experts_product",
              "experts_product_tc", "experts_gather", "experts_combine", "latent_finish", "heads_product",
-             "sigmoid_power_decay", "clamped_glu", "row_bias", "weighted_sum", "gated_sum", "experts_mix", "rmsnorm_shift", "experts_route_plan"]
+             "sigmoid_power_decay", "clamped_glu", "row_bias", "weighted_sum", "gated_sum", "experts_mix", "rmsnorm_shift", "experts_route_plan",
+             "layernorm", "norm_merge_add", "pair_embed", "rows_cast", "scale_cap", "unit_gates", "unit_scan", "rotate_rows"]
     records, saved, graphs, turn = [], {}, runner.graphs, [0]
     runner.graphs = None
 
@@ -981,6 +983,119 @@ def run_kemirax(args):
     return 0
 
 
+PIKURAX_SIZES = {
+    "w1024": {"width": 1024, "heads": 8, "kv_heads": 4, "linear_heads": 4, "unit": 1280, "blocks": 10, "ff": 3072,
+              "experts": 16, "top": 2, "expert_ff": 1024, "shared_ff": 1024},
+    "w2048": {"width": 2048, "heads": 16, "kv_heads": 4, "linear_heads": 8, "unit": 2560, "blocks": 10, "ff": 6144,
+              "experts": 16, "top": 2, "expert_ff": 2048, "shared_ff": 2048},
+}
+PIKURAX_CHUNK = 1024
+
+
+def pikurax_config(z):
+    """Eight layer runs (six layers, two of them run twice, as Malazen's of this file): four runs pair chunked attention
+    with the recurrent unit, four the biased attention with retention; heads of 128 and the linear heads are Malazen's;
+    two layers have Malazen's dense feed-forward, the others experts whose chosen two and the shared one have its weights."""
+    dense = {"kind": "dense", "ff": z["ff"]}
+    moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]}, "router": {"experts": z["experts"], "top": z["top"]},
+           "shared": {"ff": z["shared_ff"]}}
+    left = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": 128, "vdim": 128, "scale": 128 ** -0.5}
+    one = {"left": dict(left, rot={"dims": 64, "base": 500000.0}, mask={"size": PIKURAX_CHUNK}),
+           "right": {"width": z["unit"], "blocks": z["blocks"], "conv": 4}}
+    two = {"left": dict(left, q_temp={"coef": 0.1, "every": 1024}, softcap=30.0),
+           "right": {"heads": z["linear_heads"], "dim": 128, "vdim": 128, "rot": {"dims": 64, "base": 1000000.0},
+                     "decay": [1.0 - 2.0 ** (-5 - h) for h in range(z["linear_heads"])]}}
+    kinds = [("parallel", one, dense), ("parallel_2", two, moe), ("parallel", one, moe), ("parallel_2", two, dense),
+             ("parallel", one, moe), ("parallel_2", two, moe)]
+    return {"architecture": "Pikurax", "vocab": DESIGN_VOCAB, "width": z["width"], "norm": {"eps": 1e-6}, "max_positions": 4096,
+            "embedding": {"scale": 16.0, "bigram": {"buckets": 65521, "mul_prev": 127, "mul_cur": 17}},
+            "loop": {"start": 1, "stop": 3, "times": 2}, "logit_scale": 1.0, "logit_softcap": 30.0,
+            "layers": [{"type": t, "mixer": json.loads(json.dumps(m)), "mlp": json.loads(json.dumps(f))} for t, m, f in kinds]}
+
+
+def run_pikurax(args):
+    pk = peaks()
+    tokens, batch, context = PREFILL_TOKENS, 8, DESIGN_CONTEXT
+    sizes = {}
+    clocks = ClockSampler()
+    clocks.start()
+    for size, z in PIKURAX_SIZES.items():
+        mz = MALAZEN_SIZES[size]
+        malazen, _ = malazen_configs(mz)
+        row = {"pikurax": measure_design(pikurax_config(z), args, tokens, batch, context),
+               "malazen": measure_design(malazen, args, tokens, batch, context)}
+        k, m = row["pikurax"], row["malazen"]
+        w, H, G, LH, C, ff = z["width"], z["heads"], z["kv_heads"], z["linear_heads"], z["unit"], z["ff"]
+        R, DR, DP, DV = MALAZEN_RANK, MALAZEN_ROT, MALAZEN_PLAIN, MALAZEN_VALUE
+        D = -(-(R + DR) // 16) * 16
+        # layer runs: parallel x4 (layers 0, 2, 2 again, 4), parallel_2 x4 (1, 1 again, 3, 5); dense on runs of layers 0 and 3
+        n_one, n_two, n_dense, n_moe = 4, 4, 2, 6
+        one_cols = (H + 2 * G) * 128 + H * 128 + 2 * C + C
+        two_cols = (H + 2 * G) * 128 + H * 128 + 4 * LH * 128 + LH * 128
+        moe_cols = z["experts"] + 8 + 2 * z["shared_ff"] + z["shared_ff"]
+        flops_k = 2 * tokens * w * (n_one * one_cols + n_two * two_cols + n_dense * 3 * ff + n_moe * moe_cols + 2 * 2 * w) \
+            + 2 * DESIGN_VOCAB * w
+        MH, MG, MLH, MQH, mff = mz["heads"], mz["kv_heads"], mz["linear_heads"], mz["latent_heads"], mz["ff"]
+        par_cols = (MH + 2 * MG) * 128 + MH * 128 + (2 * MLH * 128 + 2 * MLH * 128 + 64) + MLH * 128
+        mlat_cols = MQH * (DP + DR) + R + DR + MQH * DV
+        flops_m = 2 * tokens * (3 * par_cols * w + 5 * mlat_cols * w + 8 * 3 * mff * w) + 2 * DESIGN_VOCAB * w
+        pairs_full = tokens * (tokens + 1) // 2
+        pairs_chunk = sum(i % PIKURAX_CHUNK + 1 for i in range(tokens))
+        pairs_win = sum(min(i + 1, MALAZEN_WINDOW) for i in range(tokens))
+        att_k = 4 * H * 128 * (n_one * pairs_chunk + n_two * pairs_full)
+        att_m = 3 * 4 * pairs_full * MH * 128 + 5 * 4 * pairs_win * MQH * D
+        flops_up = 2 * tokens * z["top"] * 2 * z["expert_ff"] * w * n_moe
+        flops_down = 2 * tokens * z["top"] * z["expert_ff"] * w * n_moe
+        gates_flops = n_one * 2 * tokens * 2 * C * (C // z["blocks"])
+        cache_k = 2 * batch * 2 * G * 128 * (n_one * (context % PIKURAX_CHUNK or PIKURAX_CHUNK) + n_two * context)
+        cache_m = 2 * batch * (3 * context * 2 * MG * 128 + 5 * min(context, MALAZEN_WINDOW) * 2 * D)
+        state_k = 2 * 4 * batch * n_two * LH * 128 * 128
+        state_m = 2 * 4 * batch * 3 * MLH * 128 * 128
+        stream = 4 * tokens * w                     # one float32 pass over the step's rows
+
+        def frac(amount, ms, peak):
+            return round(amount / (ms * 1e-3) / peak, 4) if ms else None
+
+        def ms_of(kernels, *names):
+            return sum(kernels.get(n, 0.0) for n in names)
+
+        tf, bw = pk["bf16_tflops"] * 1e12, pk["hbm_gbs"] * 1e9
+        products = ("gemm_nt_tc", "gemm_nt_tc_rmsnorm")
+        attention = ("attention_tile", "attention_prefill_tc")
+        decode_attention = ("attention_decode", "attention_decode_mma", "attention_tile")
+        kp, mp, kd, md = k["prefill_kernels_ms"], m["prefill_kernels_ms"], k["decode_kernels_ms"], m["decode_kernels_ms"]
+        row["like_kernels_fraction_of_measured_peak [pikurax, malazen]"] = {
+            "prefill: products (tensor cores)": [frac(flops_k, ms_of(kp, *products), tf), frac(flops_m, ms_of(mp, *products), tf)],
+            "prefill: attention": [frac(att_k, ms_of(kp, *attention), tf), frac(att_m, ms_of(mp, *attention), tf)],
+            "prefill: retention's rule beside the gated linear rule, microseconds a token and layer run": [
+                round(ms_of(kp, "gla_rule") * 1e3 / (n_two * tokens), 4), round(ms_of(mp, "gla_rule") * 1e3 / (3 * tokens), 4)],
+            "prefill: the recurrent unit's walk beside the gated linear rule, microseconds a token and layer run": [
+                round(ms_of(kp, "unit_scan") * 1e3 / (n_one * tokens), 4), round(ms_of(mp, "gla_rule") * 1e3 / (3 * tokens), 4)],
+            "prefill: the unit's gates (float32 on the CUDA cores), of the bf16 peak (no like kernel in malazen)": [
+                frac(gates_flops, ms_of(kp, "unit_gates"), tf), None],
+            "prefill: experts' first product (no like kernel in malazen)": [frac(flops_up, ms_of(kp, "experts_up"), tf), None],
+            "prefill: experts' second product (no like kernel in malazen)": [frac(flops_down, ms_of(kp, "experts_down"), tf), None],
+            "prefill: gated activations (bytes read and written)": [
+                frac(tokens * (8 + 2) * (n_dense * ff + n_moe * (z["top"] * z["expert_ff"] + z["shared_ff"])), ms_of(kp, "clamped_glu"), bw),
+                frac(8 * tokens * mff * (8 + 2), ms_of(mp, "clamped_glu"), bw)],
+            "prefill: norm in front of a sublayer (pikurax: layernorm; malazen: rmsnorm; float32 read, bfloat16 written)": [
+                frac(16 * tokens * w * 6, ms_of(kp, "layernorm"), bw), frac(16 * tokens * w * 6, ms_of(mp, "rmsnorm"), bw)],
+            "prefill: a sublayer's closing kernel (pikurax: norm_merge_add, 4 passes for a mixer and 3 for a feed-forward; malazen: weighted_sum, 4)": [
+                frac((8 * 4 + 8 * 3) * stream, ms_of(kp, "norm_merge_add"), bw), frac(3 * 4 * stream, ms_of(mp, "weighted_sum"), bw)],
+            "decode: attention (bytes of cache)": [frac(cache_k, ms_of(kd, *decode_attention), bw),
+                                                   frac(cache_m, ms_of(md, *decode_attention), bw)],
+            "decode: linear rule (bytes of state)": [frac(state_k, ms_of(kd, "gla_rule"), bw), frac(state_m, ms_of(md, "gla_rule"), bw)],
+        }
+        sizes[size] = row
+    clock = clocks.stop()
+    print(json.dumps({
+        "metric": "prefill of 2,048 tokens and decode at batch 8, context 2,048: Pikurax beside Malazen at equal size",
+        "unit": "ms, tok/s", "n_gpus": 1, "dtype": "bf16", "data": "synthetic", "impl": "ours", "clocks": clock,
+        "peaks": pk, "layer_runs": 8, "vocab": DESIGN_VOCAB, "sizes": sizes,
+    }))
+    return 0
+
+
 # ---------------------------------------------------------------------------
 # the reference arm: LockStep itself, unmodified, from baseline/_ref
 # ---------------------------------------------------------------------------
@@ -1150,9 +1265,9 @@ def main():
     ap.add_argument("--no-fp32", action="store_true", help="skip the float32 points")
     ap.add_argument("--only", default="", choices=["", "decode", "prefill"],
                     help="time only this part and print a short line (for profiling a small case)")
-    ap.add_argument("--workload", default="decode", choices=["decode", "mixed", "designs", "malazen", "kemirax"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "mixed", "designs", "malazen", "kemirax", "pikurax"],
                     help="mixed: a continuous batch of 64 requests through the entry point; designs: the Sevipel "
-                         "design beside Qwen3 layers of equal size, with every kernel's time; malazen, kemirax: the same "
+                         "design beside Qwen3 layers of equal size, with every kernel's time; malazen, kemirax, pikurax: the same "
                          "for those designs")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"],
                     help="element type of the --only runs (the full line always reports both)")
@@ -1175,6 +1290,8 @@ def main():
         return run_malazen(args)
     if args.workload == "kemirax":
         return run_kemirax(args)
+    if args.workload == "pikurax":
+        return run_pikurax(args)
     return run_ours(args)
 
 

@@ -109,6 +109,13 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
+// tanh x on the special-function unit, one instruction
+__device__ __forceinline__ float tanh_approx(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // lg2 x on the special-function unit, one instruction (inputs here are >= 1)
 __device__ __forceinline__ float lg2(float x) {
   float y;
@@ -161,14 +168,16 @@ struct Item {
 // EXTRAS: the scores may get a bias that grows with the logarithm of the distance of key and query taken
 // off (slopes[head] x ln(1 + log_rates[head] x distance): in the units of the exponentials,
 // slopes[head] x lg2(1 + log_rates[head] x distance), one more special-function instruction a score),
-// and the softmax's denominator one more term exp(sinks[head]) at the end of a row.
+// and the softmax's denominator one more term exp(sinks[head]) at the end of a row.  With slopes and no log_rates the
+// bias is slopes[head] x distance, and with cap_log2 > 0 (a cap times lg2 e) the scaled score first becomes
+// cap tanh(score / cap): one tanh.approx a score, again in the units of the exponentials.
 template <int HALVES, bool EXTRAS>
 __global__ void __launch_bounds__(THREADS, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
                             __nv_bfloat16* __restrict__ out, const int* __restrict__ work, int n_work,
                             const int* __restrict__ block_table, int table_stride, int nq, int nkv, int page_size,
                             int num_pages, int window, float scale_log2, const float* __restrict__ slopes,
-                            const float* __restrict__ log_rates, const float* __restrict__ sinks, int* err) {
+                            const float* __restrict__ log_rates, const float* __restrict__ sinks, float cap_log2, int* err) {
   ls_dependency_trigger();
   constexpr int D = HALVES * 64;
   constexpr int KV_BYTES = HALVES * HALF_BYTES;          // K (or V) of one tile; also Q
@@ -426,12 +435,16 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       const int lo_last = ls_first_key(pos_last, window);
       float m_ref = -CUDART_INF_F, l_run = 0.f;
       float bias_a = 0.f, bias_b = 0.f;
-      bool biased = false;
+      bool biased = false, linear = false;
       if constexpr (EXTRAS) {
         if (log_rates != nullptr) {
           bias_a = slopes[I.h];
           bias_b = log_rates[I.h];
           biased = true;
+        } else if (slopes != nullptr || cap_log2 > 0.f) {
+          bias_a = slopes != nullptr ? slopes[I.h] * 1.4426950408889634f : 0.f;      // the slope in the exponentials' units
+          bias_b = cap_log2 > 0.f ? scale_log2 / cap_log2 : 0.f;                     // score -> score x scale / cap
+          biased = linear = true;
         }
       }
       // with a bias the scores are put into the exponentials' units as they are read, and no scale is left
@@ -448,7 +461,17 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         for (int q0 = 0; q0 < HC; q0 += 32) tmem_ld32(lane_base + S_COL + s * BLOCK_N + group * HC + q0, sc + q0);
         tmem_ld_wait();
         if constexpr (EXTRAS) {
-          if (biased) {
+          if (biased && linear) {
+            const float d0 = (float)(pos - c0);
+            const bool capped = cap_log2 > 0.f;
+#pragma unroll
+            for (int jj = 0; jj < HC; ++jj) {
+              const float dist = fmaxf(d0 - (float)jj, 0.f);
+              const float raw = __uint_as_float(sc[jj]);
+              const float v = capped ? cap_log2 * tanh_approx(raw * bias_b) : raw * scale_log2;
+              sc[jj] = __float_as_uint(fmaf(-bias_a, dist, v));
+            }
+          } else if (biased) {
             const float d0 = (float)(pos - c0);        // distance of this thread's first key (masked keys: clamped)
 #pragma unroll
             for (int jj = 0; jj < HC; ++jj) {
@@ -1105,7 +1128,7 @@ int pair_heads = 1;
 template <int HALVES>
 int launch(const CUtensorMap& map_q, const CUtensorMap& map_kv, void* out, const int* work, int n_work,
            const int* block_table, int table_stride, int nq, int nkv, int page_size, int num_pages, int window,
-           float scale, const float* slopes, const float* log_rates, const float* sinks, int* err,
+           float scale, const float* slopes, const float* log_rates, const float* sinks, float softcap, int* err,
            cudaStream_t stream) {
   constexpr int KV_BYTES = HALVES * HALF_BYTES;
   const size_t smem = (size_t)KV_BYTES * (1 + 2 * STAGES) + 256 + 3 * 128 * GROUPS * 4 + 1024;
@@ -1118,13 +1141,13 @@ int launch(const CUtensorMap& map_q, const CUtensorMap& map_kv, void* out, const
       return LS_E_SMEM;
     configured = true;
   }
-  if (log_rates != nullptr || sinks != nullptr) {
+  if (slopes != nullptr || sinks != nullptr || softcap > 0.f) {
     // a bias on the scores or a sink: the kernel with a head a block knows them
     const long long items = (long long)n_work * nq;
     const int blocks = items < sm_count() ? (int)items : sm_count();
     LS_COUNT(LS_K_ATTENTION_PREFILL_TC), ls_launch(attention_prefill_tc_kernel<HALVES, true>, dim3(blocks), THREADS, smem, stream, map_q, map_kv,
               (__nv_bfloat16*)out, work, n_work, block_table, table_stride, nq, nkv, page_size, num_pages, window,
-              scale * 1.4426950408889634f, slopes, log_rates, sinks, err);
+              scale * 1.4426950408889634f, slopes, log_rates, sinks, softcap > 0.f ? softcap * 1.4426950408889634f : 0.f, err);
     return ls_launch_status();
   }
   // two heads of a key head in a block where the group size is even and there are items enough
@@ -1152,7 +1175,7 @@ int launch(const CUtensorMap& map_q, const CUtensorMap& map_kv, void* out, const
   const int blocks = items < sm_count() ? (int)items : sm_count();
   LS_COUNT(LS_K_ATTENTION_PREFILL_TC), ls_launch(attention_prefill_tc_kernel<HALVES, false>, dim3(blocks), THREADS, smem, stream, map_q, map_kv, (__nv_bfloat16*)out, work, n_work,
             block_table, table_stride, nq, nkv, page_size, num_pages, window, scale * 1.4426950408889634f,
-            (const float*)nullptr, (const float*)nullptr, (const float*)nullptr, err);
+            (const float*)nullptr, (const float*)nullptr, (const float*)nullptr, 0.f, err);
   return ls_launch_status();
 }
 
@@ -1168,9 +1191,9 @@ LS_API void ls_set_attention_prefill_pairs(int mode) { pair_heads = mode < 0 ? 0
 LS_API int ls_attention_prefill_tc(const void* q, const void* pages, void* out, int tokens, const int* work,
                                    int n_work, const int* block_table, int table_stride, int nq, int nkv, int d,
                                    int page_size, int num_pages, int window, float scale, const float* slopes,
-                                   const float* log_rates, const float* sinks, int* err, cudaStream_t stream) {
+                                   const float* log_rates, const float* sinks, float softcap, int* err, cudaStream_t stream) {
   if (n_work <= 0 || tokens <= 0) return 0;
-  if ((slopes != nullptr) != (log_rates != nullptr)) return LS_E_SIZE;      // a linear bias alone: the CUDA-core kernels
+  if (log_rates != nullptr && (slopes == nullptr || softcap > 0.f)) return LS_E_SIZE;
   if (nq <= 0 || nkv <= 0 || nq % nkv || n_work > 65535) return LS_E_SIZE;
   if (d != 64 && d != 128) return LS_E_SIZE;
   if (page_size != 8 && page_size != 16 && page_size != 32 && page_size != 64 && page_size != 128) return LS_E_SIZE;
@@ -1182,9 +1205,9 @@ LS_API int ls_attention_prefill_tc(const void* q, const void* pages, void* out, 
   if (!encode(&map_kv, pages, (uint64_t)d, (uint64_t)rows, page_size < BLOCK_N ? page_size : BLOCK_N)) return LS_E_SIZE;
   if (d == 64)
     return launch<1>(map_q, map_kv, out, work, n_work, block_table, table_stride, nq, nkv, page_size, num_pages,
-                     window, scale, slopes, log_rates, sinks, err, stream);
+                     window, scale, slopes, log_rates, sinks, softcap, err, stream);
   return launch<2>(map_q, map_kv, out, work, n_work, block_table, table_stride, nq, nkv, page_size, num_pages,
-                   window, scale, slopes, log_rates, sinks, err, stream);
+                   window, scale, slopes, log_rates, sinks, softcap, err, stream);
 }
 
 LS_API const char* ls_constants_attention_prefill_tc() {

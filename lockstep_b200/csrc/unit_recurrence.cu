@@ -181,7 +181,7 @@ __global__ void __launch_bounds__(128) rotate_rows_kernel(RotateArgs r, int* err
   const int Kd = r.heads * r.dk, Vd = r.heads * r.dv, half = r.rot_dim >> 1;
   float* dst = r.out + (int64_t)t * (2 * Kd + Vd);
   int pos = r.positions[t];
-  if (pos < 0 || pos >= r.max_positions) {
+  if (half > 0 && (pos < 0 || pos >= r.max_positions)) {
     if (threadIdx.x == 0) ls_record_fault(err, LS_DEV_POSITION_RANGE, t);
     pos = 0;
   }

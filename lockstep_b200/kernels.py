@@ -92,7 +92,7 @@ _SIGNATURES["tc"] = {
                                 c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p],
     "ls_attention_prefill_tc_tile_tokens": [],
     "ls_attention_prefill_tc": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
-                                c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+                                c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p],
     "ls_gemm_nt_tc_qkv_heads": [c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_int, c_float, c_void_p,
                                 c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                 c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
@@ -586,12 +586,12 @@ def attention_prefill_tc_tile_tokens() -> int:
 
 
 def attention_prefill_tc(q, pages, out, work, n_work, block_table, nq, nkv, d, window, scale, err,
-                         slopes=None, log_rates=None, sinks=None) -> bool:
+                         slopes=None, log_rates=None, sinks=None, softcap: float = 0.0) -> bool:
     """Attention of prompt portions on tcgen05 (csrc/attention_prefill_tc.cu): bfloat16, head
     size 64 or 128, work items of up to 128 tokens; ``slopes`` with ``log_rates`` (the bias that
-    grows with the logarithm of the distance) and ``sinks`` as in ``attention_tile``.  Returns
-    False (nothing launched) for anything else."""
-    if (slopes is None) != (log_rates is None):
+    grows with the logarithm of the distance), ``slopes`` alone (the bias linear in the distance), ``softcap`` and
+    ``sinks`` as in ``attention_tile``.  Returns False (nothing launched) for anything else."""
+    if log_rates is not None and (slopes is None or softcap):
         return False
     if q.dtype != torch.bfloat16 or not USE_TENSOR_CORES[0]:
         return False
@@ -599,7 +599,7 @@ def attention_prefill_tc(q, pages, out, work, n_work, block_table, nq, nkv, d, w
         _dev(q, "q"), _dev(pages, "pages", q.dtype), _dev(out, "out", q.dtype), q.shape[0],
         _dev(work, "work", torch.int32), n_work, _dev(block_table, "block_table", torch.int32),
         block_table.shape[-1], nq, nkv, d, pages.shape[3], pages.shape[0], int(window), float(scale),
-        _slopes(slopes, nq), _slopes(log_rates, nq), _slopes(sinks, nq), _dev(err, "err", torch.int32), _stream())
+        _slopes(slopes, nq), _slopes(log_rates, nq), _slopes(sinks, nq), float(softcap), _dev(err, "err", torch.int32), _stream())
     if status in (-2, -3):
         return False
     _check(status, "attention_prefill_tc")

@@ -56,13 +56,14 @@ def _f32(t: torch.Tensor) -> torch.Tensor:
 class ScoreExtras:
     """What the attention kernels add to plain scaled scores: a bias that grows with the distance
     of key and query (``slopes`` alone: linear; with ``log_rates``: logarithmic) and sinks.  The
-    tensor-core kernels know the logarithmic bias and sinks; a linear bias keeps the attention on
-    the CUDA-core kernels."""
+    tensor-core kernel of prompt portions knows all of them; that of decoded tokens the logarithmic bias (a linear
+    bias or a cap keeps decoded tokens on the CUDA-core kernels)."""
 
     def __init__(self, slopes=None, log_rates=None, sinks=None, softcap: float = 0.0):
         self.slopes, self.log_rates, self.sinks, self.softcap = slopes, log_rates, sinks, float(softcap or 0.0)
 
     def tensor_cores(self) -> bool:
+        """Whether the tensor-core kernel of decoded tokens knows these extras (that of prompt portions knows all)."""
         return (self.slopes is None or self.log_rates is not None) and not self.softcap
 
 
@@ -76,11 +77,11 @@ def attend(rt: Runtime, q, ctx, cache, nq: int, nkv: int, d: int, window: int, s
     tensor_core_attention = not exact and extras.tensor_cores()
     attn = rt.rows(t, nq * d)
     plan, done = None, False
-    if tensor_core_attention and d in (64, 128):
+    if not exact and d in (64, 128):
         plan = ctx.attention_plan(window, K.attention_prefill_tc_tile_tokens())
         done = not plan.n_tile or K.attention_prefill_tc(
             q, cache.pages, attn, plan.tile_work, plan.n_tile, cache.block_table, nq, nkv, d,
-            window, scale, rt.err, extras.slopes, extras.log_rates, extras.sinks)
+            window, scale, rt.err, extras.slopes, extras.log_rates, extras.sinks, softcap=extras.softcap)
     if not done:
         plan = ctx.attention_plan(window)
         if plan.n_tile:

@@ -236,11 +236,18 @@ def gated_unit(x, w, p, act):
     return (act(x @ w[p + ".gate"].T) * (x @ w[p + ".up"].T)) @ w[p + ".down"].T
 
 
+# a list here collects, per routed layer run, the smallest gap between the last chosen and the first rejected logit
+ROUTING_GAPS = None
+
+
 def route(x, w, p, top):
     """Chosen experts [n, top] (largest logits first, ties to the lower index) and their weights: the softmax over
     the chosen logits alone."""
     z = x @ w[p + ".router"].T
     order = torch.sort(z, dim=-1, descending=True, stable=True).indices[:, :top]
+    if ROUTING_GAPS is not None and z.shape[1] > top:
+        ranked = torch.sort(z, dim=-1, descending=True).values
+        ROUTING_GAPS.append(float((ranked[:, top - 1] - ranked[:, top]).min()))
     return order, torch.softmax(torch.gather(z, 1, order), dim=-1), z
 
 
@@ -296,3 +303,17 @@ def forward(tokens, w, cfg, dtype=torch.float64, streams=False):
     if cap:
         logits = cap * torch.tanh(logits / cap)
     return (logits, torch.stack(kept)) if streams else logits
+
+
+def model_logits(folder, tokens, dtype=torch.float64, edit=None):
+    """Logits of the model stored in ``folder`` (config.json, model.safetensors) for the whole sequence.
+    ``edit(config)`` may change the configuration first (a test that asks what a mechanism is worth)."""
+    import json
+    from pathlib import Path
+
+    from safetensors.torch import load_file
+
+    cfg = json.loads((Path(folder) / "config.json").read_text())
+    if edit is not None:
+        edit(cfg)
+    return forward(tokens, load_file(str(Path(folder) / "model.safetensors")), cfg, dtype)

@@ -1,0 +1,594 @@
+"""Pikurax on the device against the plain implementation: the kernels of every mechanism alone (layer norm, the
+closing kernel of normed parallel mixers, the pair embedding and the token it carries, the recurrent unit's gates and
+walk across calls, the rotation in front of retention, routing by a softmax over the chosen logits, the gated units'
+activations, the injection), one-layer models, and whole models cut in four ways (whole prompts; a prompt and then
+token by token; portions down to one and two tokens; up to three live requests, portions of some beside single
+tokens of others, on so few pages and slots that they are used again), in float32 and bfloat16; weights made so
+that a chunk's edge, a far key, a sink, a lost state, a lost previous token shows; greedy generation through the entry
+point and the scheduler; the command line; the trace runner."""
+
+from __future__ import annotations
+
+import json
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import helpers as H
+import pikurax_models as M
+from plain import pikurax_plain as plain
+
+pytestmark = pytest.mark.gpu
+
+ROOT = Path(__file__).resolve().parent.parent
+DEV = "cuda:0"
+F32, BF16 = torch.float32, torch.bfloat16
+
+
+def make_runner(folder, dtype, page, steps=None, max_live=3, num_pages=None, **kw):
+    from lockstep_b200.engine import ModelRunner
+
+    if num_pages is None:
+        num_pages = H.max_live_tokens(steps, round_to=page) // page
+    return ModelRunner(folder, dtype=dtype, num_pages=num_pages, page_size=page, max_live=max_live,
+                       max_seq_len=1024, **kw)
+
+
+PLANS = {
+    "whole": H.plan_whole,
+    "then_single": lambda r: H.plan_bulk_then_single(r, tail=70),
+    "portions": lambda r: H.plan_portions(r, sizes=(7, 2, 17, 3, 33, 2, 5, 64, 1, 2, 150)),
+    "mixed": lambda r: H.plan_mixed(r, max_live=3),
+}
+
+
+def _tol(dtype):
+    return 2e-5 if dtype == F32 else 2e-2
+
+
+# ---------------------------------------------------------------------------
+# kernels alone
+# ---------------------------------------------------------------------------
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("width", [72, 52, 320, 7, 1024])
+def test_layer_norm(dtype, width):
+    from lockstep_b200 import kernels as K
+
+    torch.manual_seed(width)
+    x = (torch.randn(19, width, device=DEV) * 3 + 5).contiguous()       # a mean far from zero
+    gain = torch.randn(width, device=DEV)
+    err = K.new_error_word(DEV)
+    out = torch.empty(19, width, dtype=dtype, device=DEV)
+    K.layernorm(x, gain, out, 1e-5, err)
+    want = plain.layer_norm(x.double().cpu(), gain.double().cpu(), 1e-5)
+    assert float((out.double().cpu() - want).abs().max()) <= _tol(dtype) * float(want.abs().max())
+    rows = torch.tensor([4, 0, 18], dtype=torch.int32, device=DEV)
+    some = torch.empty(3, width, dtype=dtype, device=DEV)
+    K.layernorm(x, gain, some, 1e-5, err, rows)
+    assert torch.equal(some, out[rows.long()])
+    K.raise_on_fault(err)
+
+
+@pytest.mark.parametrize("branches, normed, post", [(2, True, True), (2, True, False), (1, False, True), (3, True, True)])
+@pytest.mark.parametrize("width", [72, 52, 256])
+def test_closing_kernel_of_normed_mixers(branches, normed, post, width):
+    from lockstep_b200 import kernels as K
+
+    torch.manual_seed(width + branches)
+    b = torch.randn(branches, 11, width, device=DEV) * torch.tensor([0.01, 30.0, 1.0][:branches], device=DEV)[:, None, None]
+    gains = torch.randn(branches, width, device=DEV) if normed else None
+    post_gain = torch.randn(width, device=DEV) if post else None
+    residual = torch.randn(11, width, device=DEV)
+    want = residual.double().cpu()
+    merged = sum((plain.rms_unit(b[i].double().cpu(), 1e-6) * gains[i].double().cpu()) if normed else b[i].double().cpu()
+                 for i in range(branches)) * 0.5
+    want = want + (plain.layer_norm(merged, post_gain.double().cpu(), 3e-6) if post else merged)
+    K.norm_merge_add(residual, b.contiguous(), gains, 0.5, post_gain, 1e-6, 3e-6)
+    assert float((residual.double().cpu() - want).abs().max()) <= 2e-5 * float(want.abs().max())
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+def test_pair_embedding_carries_the_last_token(dtype):
+    from lockstep_b200 import kernels as K
+
+    torch.manual_seed(3)
+    vocab, width, buckets = 50, 24, 13
+    table = torch.randn(vocab, width, device=DEV).to(dtype)
+    pairs = torch.randn(buckets + 1, width, device=DEV).to(dtype)
+    err = K.new_error_word(DEV)
+    carried = torch.zeros(5, 1, dtype=torch.int32, device=DEV)
+    seqs = {0: H.random_tokens(9, vocab, 1), 3: H.random_tokens(7, vocab, 2), 4: H.random_tokens(1, vocab, 5)}
+    bg = {"buckets": buckets, "mul_prev": 11, "mul_cur": 5}
+    want = {s: table[torch.tensor(t)].double().cpu() * 2.5 + pairs[torch.tensor(plain.bigram_rows(t, bg))].double().cpu()
+            for s, t in seqs.items()}
+    got = {s: [] for s in seqs}
+    # three calls: portions of the requests side by side, one of a single token, one request left out of a call
+    for cut in ({0: (0, 4), 3: (0, 1), 4: (0, 1)}, {3: (1, 2)}, {0: (4, 9), 3: (2, 7)}):
+        ids, slots = [], []
+        for s, (a, b) in cut.items():
+            ids += seqs[s][a:b]
+            slots += [s] * (b - a)
+        out = torch.empty(len(ids), width, device=DEV)
+        K.pair_embed(torch.tensor(ids, dtype=torch.int32, device=DEV), torch.tensor(slots, dtype=torch.int32, device=DEV),
+                     carried, table, pairs, out, 2.5, 11, 5, err)
+        at = 0
+        for s, (a, b) in cut.items():
+            got[s].append(out[at:at + b - a].double().cpu())
+            at += b - a
+    K.raise_on_fault(err)
+    for s in seqs:
+        assert float((torch.cat(got[s]) - want[s]).abs().max()) <= 1e-5, s
+    assert carried.view(-1).tolist() == [seqs[0][-1] + 1, 0, 0, seqs[3][-1] + 1, seqs[4][-1] + 1]
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("width, blocks, taps", [(40, 5, 4), (26, 2, 1), (13, 13, 3), (320, 1, 2), (96, 3, 8)])
+def test_recurrent_unit_across_calls(dtype, width, blocks, taps):
+    """Gates, decays and the walk of the unit for three requests in portions across calls (one of a single token, one
+    shorter than the convolution), against the plain functions on the whole sequences; lam so negative that S keeps
+    what the first tokens gave it."""
+    from lockstep_b200 import kernels as K
+
+    torch.manual_seed(width + taps)
+    bw = width // blocks
+    rnd = lambda *s: torch.randn(*s, device=DEV)
+    w_r, w_i = (rnd(blocks, bw, bw) * bw ** -0.5).to(dtype), (rnd(blocks, bw, bw) * bw ** -0.5).to(dtype)
+    b_r, b_i, x_bias, y_bias, conv_b = rnd(width), rnd(width), rnd(width) * 0.1, rnd(width) * 0.1, rnd(width) * 0.1
+    conv_w, lam = rnd(width, taps) * 0.5, rnd(width) - 4.0
+    x_at = -(-width // 8) * 8
+    lengths = {0: 37, 2: 12, 1: 5}
+    proj = {s: (rnd(n, x_at + width)).to(dtype) for s, n in lengths.items()}
+    want = {}
+    for s, p in proj.items():
+        pd = p.double().cpu()
+        y = plain.gelu_tanh(pd[:, :width] + y_bias.double().cpu())
+        u = plain.causal_conv(pd[:, x_at:] + x_bias.double().cpu(), conv_w.double().cpu(), conv_b.double().cpu())
+        ub = u.view(-1, blocks, bw)
+        r = torch.sigmoid(torch.einsum("boi,nbi->nbo", w_r.double().cpu(), ub).reshape(-1, width) + b_r.double().cpu())
+        i = torch.sigmoid(torch.einsum("boi,nbi->nbo", w_i.double().cpu(), ub).reshape(-1, width) + b_i.double().cpu())
+        S, _ = plain.gated_unit_recurrence(u, r, i, lam.double().cpu())
+        want[s] = S * y
+    state = torch.zeros(4, taps * width, device=DEV)
+    err = K.new_error_word(DEV)
+    rate = torch.nn.functional.softplus(lam).contiguous()
+    got = {s: [] for s in lengths}
+    cuts = ({0: (0, 9), 2: (0, 1), 1: (0, 2)}, {0: (9, 10), 2: (1, 3)}, {0: (10, 37), 2: (3, 12), 1: (2, 5)})
+    for cut in cuts:
+        rows = torch.cat([proj[s][a:b] for s, (a, b) in cut.items()]).contiguous()
+        slots = torch.tensor([s for s, (a, b) in cut.items() for _ in range(b - a)], dtype=torch.int32, device=DEV)
+        n = rows.shape[0]
+        a_, b_ = torch.empty(n, width, device=DEV), torch.empty(n, width, device=DEV)
+        K.unit_gates(rows, x_at, x_bias, conv_w.contiguous(), conv_b, state, slots, w_r.transpose(1, 2).contiguous(),
+                     w_i.transpose(1, 2).contiguous(), b_r, b_i, rate, a_, b_, blocks, taps, 8.0)
+        portions = torch.empty(1 + 3 * 4, dtype=torch.int32, device=DEV)
+        K.find_portions(slots, portions, 4, err)
+        out = torch.empty(n, width, dtype=dtype, device=DEV)
+        K.unit_scan(portions, 4, a_, b_, rows, 0, x_at, y_bias, x_bias, state, out, taps)
+        at = 0
+        for s, (lo, hi) in cut.items():
+            got[s].append(out[at:at + hi - lo].double().cpu())
+            at += hi - lo
+    K.raise_on_fault(err)
+    for s in lengths:
+        g = torch.cat(got[s])
+        assert float((g - want[s]).abs().max()) <= _tol(dtype) * (1 + float(want[s].abs().max())), s
+    assert float(state[3].abs().max()) == 0.0                        # a slot nobody used
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("heads, dk, dv, rot", [(3, 8, 24, 4), (2, 16, 8, 16), (1, 6, 10, 2), (4, 32, 64, 32), (2, 40, 16, 0)])
+def test_retention_across_calls(dtype, heads, dk, dv, rot):
+    from lockstep_b200 import kernels as K
+
+    torch.manual_seed(heads * dk)
+    Kd, Vd = heads * dk, heads * dv
+    decay = [1.0, 0.999, 0.97, 0.5][:heads]
+    ang = torch.arange(64, dtype=torch.float64)[:, None] * torch.tensor([500.0 ** (-2.0 * i / max(rot, 1)) for i in range(rot // 2)],
+                                                                         dtype=torch.float64)[None]
+    cos, sin = ang.cos().float().to(DEV).contiguous(), ang.sin().float().to(DEV).contiguous()
+    lengths = {1: 41, 0: 6}
+    at_k, at_v = -(-Kd // 8) * 8, 2 * (-(-Kd // 8) * 8)
+    proj = {s: torch.randn(n, at_v + Vd, device=DEV).to(dtype) for s, n in lengths.items()}
+    want = {}
+    for s, p in proj.items():
+        pd = p.double().cpu()
+        q = plain.rotate_halves(pd[:, :Kd].reshape(-1, heads, dk), 500.0, rot) if rot else pd[:, :Kd].reshape(-1, heads, dk)
+        k = pd[:, at_k:at_k + Kd].reshape(-1, heads, dk)
+        k = (plain.rotate_halves(k, 500.0, rot) if rot else k) * dk ** -0.5
+        want[s], _ = plain.retention_rule(q, k, pd[:, at_v:].reshape(-1, heads, dv), torch.tensor(decay, dtype=torch.float64))
+    state = torch.zeros(3, heads * dk * dv, device=DEV)
+    err = K.new_error_word(DEV)
+    d = torch.tensor(decay, device=DEV).repeat_interleave(dk).contiguous()
+    got = {s: [] for s in lengths}
+    for cut in ({1: (0, 17), 0: (0, 1)}, {1: (17, 18)}, {1: (18, 41), 0: (1, 6)}):
+        rows = torch.cat([proj[s][a:b] for s, (a, b) in cut.items()]).contiguous()
+        slots = torch.tensor([s for s, (a, b) in cut.items() for _ in range(b - a)], dtype=torch.int32, device=DEV)
+        pos = torch.tensor([i for s, (a, b) in cut.items() for i in range(a, b)], dtype=torch.int32, device=DEV)
+        n = rows.shape[0]
+        qkv = torch.empty(n, 2 * Kd + Vd, device=DEV)
+        K.rotate_rows(rows, 0, at_k, at_v, cos, sin, pos, qkv, heads, dk, dv, rot, dk ** -0.5, err)
+        portions = torch.empty(1 + 3 * 3, dtype=torch.int32, device=DEV)
+        K.find_portions(slots, portions, 3, err)
+        o = torch.empty(n, Vd, device=DEV)
+        K.state_rule(K.RULE_GLA, F32, portions, 3, state, qkv[:, :Kd], qkv[:, Kd:2 * Kd], qkv[:, 2 * Kd:], d, None, None, o,
+                     None, 0, 0, heads, heads, dk, dv, decay_fixed=True)
+        at = 0
+        for s, (lo, hi) in cut.items():
+            got[s].append(o[at:at + hi - lo].double().cpu().view(-1, heads, dv))
+            at += hi - lo
+    K.raise_on_fault(err)
+    for s in lengths:
+        assert float((torch.cat(got[s]) - want[s]).abs().max()) <= 2e-5 * (1 + float(want[s].abs().max())), s
+
+
+@pytest.mark.parametrize("experts, top", [(12, 3), (5, 5), (40, 4), (1, 1), (300, 7)])
+def test_routing_by_a_softmax_over_the_chosen_logits(experts, top):
+    from lockstep_b200 import kernels as K
+
+    torch.manual_seed(experts)
+    logits = torch.randn(23, experts + 3, device=DEV) * 3            # three more columns that are not experts
+    ids = torch.empty(23, top, dtype=torch.int32, device=DEV)
+    weights = torch.empty(23, top, device=DEV)
+    K.experts_route(logits, top, ids, weights, experts=experts, softmax=2)
+    z = logits[:, :experts].double().cpu()
+    order = torch.sort(z, dim=-1, descending=True, stable=True).indices[:, :top]
+    assert torch.equal(ids.cpu().long(), order)
+    assert float((weights.double().cpu() - torch.softmax(z.gather(1, order), -1)).abs().max()) <= 1e-6
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("gelu", [True, False])
+def test_gated_units_activations(dtype, gelu):
+    from lockstep_b200 import kernels as K
+
+    torch.manual_seed(5)
+    gu = (torch.randn(9, 2 * 52, device=DEV) * 3).contiguous()
+    out = torch.empty(9, 52, dtype=dtype, device=DEV)
+    K.clamped_glu(gu, None, out, float("inf"), 1.0, up_offset=0.0, gelu=gelu)
+    g, u = gu[:, :52].double().cpu(), gu[:, 52:].double().cpu()
+    want = (plain.gelu_tanh(g) if gelu else plain.silu(g)) * u
+    assert float((out.double().cpu() - want).abs().max()) <= _tol(dtype) * float(want.abs().max())
+
+
+# ---------------------------------------------------------------------------
+# one-layer models: every mechanism in the engine, in every cutting
+# ---------------------------------------------------------------------------
+
+SMALL = {
+    "chunked": [M.bare(M.chunked(3, 1, 16, 8, 24, 24, 3, 3))],
+    "chunked_heads_of_20": [M.bare(M.chunked(2, 2, 20, 10, 50, 16, 1, 4))],
+    "chunk_of_one_page": [M.bare(M.chunked(2, 1, 32, 32, 8, 8, 2, 2))],
+    "biased": [M.bare(M.biased(4, 2, 24, 16, 3, 8, 4, 24, (0.9, 0.97, 0.995)))],
+    "biased_plain": [M.bare(M.biased(2, 2, 16, 40, 2, 16, 16, 8, (0.99, 0.5), q_temp=None, softcap=None))],
+    "dense": [M.dense(M.chunked(1, 1, 16, 16, 64, 8, 1, 1), 40)],
+    "experts": [M.moe(M.chunked(1, 1, 16, 16, 64, 8, 1, 1), 6, 2, 24, shared=16)],
+    "experts_all": [M.moe(M.chunked(1, 1, 16, 16, 64, 8, 1, 1), 3, 3, 8)],
+    "looped": [M.bare(M.chunked(2, 1, 16, 8, 30, 16, 2, 2)), M.dense(M.biased(2, 1, 16, 16, 2, 8, 8, 8, (0.9, 0.99)), 24)],
+}
+SMALL_KW = {"looped": {"loop": (0, 2, 3)}, "dense": {"pairs": None}, "experts": {"logit_softcap": None}}
+
+
+@pytest.fixture(scope="module")
+def zoo(tmp_path_factory):
+    cache = {}
+
+    def get(config, dtype, lengths, seed=7, edit=None, key=None):
+        key = (key or json.dumps(config, sort_keys=True), dtype, tuple(lengths))
+        if key not in cache:
+            folder = M.make_folder(tmp_path_factory.mktemp("pikurax"), config, seed=seed, dtype=dtype, edit=edit)
+            requests, want = {}, {}
+            for i, n in enumerate(lengths):
+                # no request rests on a router's close call: another draw of tokens where float32 would decide one
+                for draw in range(20):
+                    tokens = H.random_tokens(n, config["vocab"], seed=50 + i + 1000 * draw)
+                    logits, gap = M.plain_logits_and_gap(folder, tokens)
+                    if gap > 1e-3:
+                        break
+                requests[f"r{i}"], want[f"r{i}"] = tokens, logits.float()
+            cache[key] = (folder, requests, want)
+        return cache[key]
+
+    return get
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", sorted(SMALL))
+def test_small_models_in_every_cutting(zoo, name, dtype):
+    folder, requests, want = zoo(M.layers_model(SMALL[name], **SMALL_KW.get(name, {})), dtype, [45, 130, 9, 77])
+    rows = {}
+    for plan_name, plan in PLANS.items():
+        steps = plan(requests)
+        runner = make_runner(folder, dtype, 8, steps)
+        rows[plan_name] = H.run_plan(runner, steps)
+        # (without routed experts no choice is a close call: float32 holds every row; in bfloat16 three passes over
+        # two layers bring one row in a few hundred just past the bound)
+        M.assert_close(rows[plan_name], want, dtype, f"{name}, {plan_name}",
+                       None if name.startswith("experts") else 0.0 if dtype == "float32" else 0.02)
+        runner.cache.audit()
+    if dtype == "float32":
+        # a row's arithmetic does not depend on how its request was cut or on the batch
+        for plan_name in PLANS:
+            for key, row in rows["whole"].items():
+                assert torch.equal(row, rows[plan_name][key]), (name, plan_name, key)
+
+
+LENGTHS = {"S": [70, 300, 37, 150, 129], "T": [45, 210, 90, 33, 260], "U": [40, 190, 75, 131]}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("plan_name", sorted(PLANS))
+@pytest.mark.parametrize("model", sorted(M.MODELS))
+def test_whole_models_in_every_cutting(zoo, model, plan_name, dtype):
+    config, page = M.MODELS[model]
+    folder, requests, want = zoo(config, dtype, LENGTHS[model])
+    steps = PLANS[plan_name](requests)
+    runner = make_runner(folder, dtype, page, steps)
+    rows = H.run_plan(runner, steps)
+    M.assert_close(rows, want, dtype, f"model {model}, {plan_name}",
+                   M.PERSISTENT if (model, dtype) == ("S", "bfloat16") else None)
+    runner.cache.audit()
+    if plan_name == "mixed":
+        assert runner.cache.reused_pages() > 0           # more requests than slots, and few pages
+    if plan_name == "then_single" and runner.graphs is not None:
+        assert runner.graphs.replays > 100               # decoded tokens ran as recorded steps
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_the_stream_after_every_layer_run(zoo, dtype):
+    """The residual stream after every run of a layer (a looped layer counts each time) against the plain model's."""
+    from lockstep_b200.engine.batch import StepContext, StepEntry
+
+    name = "S" if dtype == "float32" else "U"          # (no router of U has a choice: nothing to call closely)
+    config, page = M.MODELS[name]
+    folder, requests, _ = zoo(config, dtype, LENGTHS[name])
+    tokens = requests["r0"]
+    from safetensors.torch import load_file
+    _, want = plain.forward(tokens, load_file(str(folder / "model.safetensors")), json.loads((folder / "config.json").read_text()),
+                            streams=True)
+    runner = make_runner(folder, dtype, page, num_pages=16, use_graphs=False)
+    runner.open("a")
+    runner.cache.reserve("a", len(tokens))
+    runner.cache.sync()
+    ctx = StepContext([StepEntry("a", tokens, 0, [0])], [runner.cache.slots["a"]], runner.device, runner.err, runner.split_size)
+    ends, at = [], 1
+    for run in runner.spec.schedule:
+        at += (1 if run.inject else 0) + len(runner.model.blocks[run.layer].steps())
+        ends.append(at)
+    h, k = None, 0
+    for i, (_, fn) in enumerate(runner.program[:-1]):
+        h = fn(h, ctx)
+        if i + 1 in ends:
+            err = float((h.double().cpu() - want[k]).abs().max()) / float(want[k].abs().max())
+            assert err <= (2e-5 if dtype == "float32" else 5e-2), (k, err)
+            k += 1
+    assert k == len(runner.spec.schedule) == (8 if name == "S" else 4)
+
+
+# ---------------------------------------------------------------------------
+# weights that make a fault show
+# ---------------------------------------------------------------------------
+
+def _sharpen(scale):
+    def edit(tensors):
+        for name in tensors:
+            if name.endswith((".left.q", ".left.q.norm")):
+                tensors[name] = (tensors[name].float() * scale).to(tensors[name].dtype)
+    return edit
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("chunk, dim, pad", [(37, 16, 16), (64, 64, 64), (200, 64, 64), (96, 24, 32)])
+def test_sharp_softmax_at_the_edges_of_chunks(zoo, chunk, dim, pad, dtype):
+    """Queries so large that every row's softmax is a choice of one key: rows whose key is the first of their chunk,
+    rows whose best key would be the one just before it, keys hundreds of tokens back in a long chunk; a model that
+    took chunks one token longer or shorter gives other logits."""
+    from lockstep_b200 import kernels as K
+
+    config = M.layers_model([M.bare(M.chunked(2, 1, dim, dim // 2, chunk, 16, 2, 2, scale=1.0))], width=64)
+    folder, requests, want = zoo(config, dtype, [420, 75], edit=_sharpen(6.0), key=f"sharp-{chunk}-{dim}")
+    from safetensors.torch import load_file
+    w = {k: v.double() for k, v in load_file(str(folder / "model.safetensors")).items()}
+    x = plain.layer_norm(plain.embedding(requests["r0"], w, config), w["l0.norm1"], 1e-5)
+    pr = plain.chunked_attention_mixer(x, w, "l0.mix.left", config["layers"][0]["mixer"]["left"], weights=True)
+    best = pr.argmax(-1)                                              # [heads, rows]
+    rows = torch.arange(420)
+    first = rows - rows % chunk
+    assert int(((best == first[None]) & (pr.max(-1).values > 0.5) & (rows[None] > first[None])).sum()) >= 3
+    if chunk >= 200:
+        assert int(((rows[None] - best) > 150).sum()) >= 3            # keys far back inside a long chunk
+    for wrong in (chunk - 1, chunk + 1):
+        other = M.plain_logits(folder, requests["r0"], edit=lambda c: c["layers"][0]["mixer"]["left"]["mask"].update(size=wrong))
+        assert float((other.float() - want["r0"]).abs().max()) > 0.5
+    before = K.kernel_counts()
+    for plan_name, plan in PLANS.items():
+        steps = plan(requests)
+        runner = make_runner(folder, dtype, 8, steps)
+        M.assert_close(H.run_plan(runner, steps), want, dtype, f"sharp chunks of {chunk}, {plan_name}", 0.0,
+                       slack=1.0 if dtype == "float32" else 2.0)
+    after = K.kernel_counts()
+    tensor_cores = after.get("attention_prefill_tc", 0) - before.get("attention_prefill_tc", 0)
+    assert (tensor_cores > 0) == (dtype == "bfloat16" and pad == 64)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_sharp_biased_attention_reaches_far_keys_and_its_sink(zoo, dtype):
+    """Large queries against a weak distance bias: rows whose largest key lies hundreds of tokens back, rows the sink
+    takes and rows it does not; a model without the sink, the cap or the temperature gives other logits."""
+    config = M.layers_model([M.bare(M.biased(4, 2, 32, 16, 2, 8, 8, 8, (0.9, 0.99), q_temp=(0.6, 32), softcap=30.0, scale=0.5))],
+                            width=64)
+
+    def edit(tensors):
+        _sharpen(2.0)(tensors)
+        tensors["l0.mix.left.sink"] = torch.tensor([9.0, 14.0, 2.0, -3.0]).to(tensors["l0.mix.left.sink"].dtype)
+
+    folder, requests, want = zoo(config, dtype, [500, 61], edit=edit, key="sharp-biased")
+    from safetensors.torch import load_file
+    w = {k: v.double() for k, v in load_file(str(folder / "model.safetensors")).items()}
+    x = plain.layer_norm(plain.embedding(requests["r0"], w, config), w["l0.norm1"], 1e-5)
+    pr = plain.biased_attention_mixer(x, w, "l0.mix.left", config["layers"][0]["mixer"]["left"], 1e-5, weights=True)
+    rows = torch.arange(500)
+    far = (rows[None] - pr.argmax(-1) > 200) & (pr.max(-1).values > 0.3)
+    assert int(far.sum()) >= 3
+    taken = 1.0 - pr.sum(-1)                                          # what the sink took of every row
+    assert int((taken > 0.9).sum()) >= 10 and int((taken < 0.1).sum()) >= 10
+    for change in (lambda m: m.pop("softcap"), lambda m: m.pop("q_temp")):
+        other = M.plain_logits(folder, requests["r0"], edit=lambda c: change(c["layers"][0]["mixer"]["left"]))
+        assert float((other.float() - want["r0"]).abs().max()) > 0.5
+    for plan_name, plan in PLANS.items():
+        steps = plan(requests)
+        runner = make_runner(folder, dtype, 16, steps)
+        M.assert_close(H.run_plan(runner, steps), want, dtype, f"sharp biased attention, {plan_name}", 0.0,
+                       slack=1.0 if dtype == "float32" else 2.0)
+
+
+def _remember(tensors):
+    for name in tensors:
+        if name.endswith(".right.lam"):
+            tensors[name] = torch.full_like(tensors[name], -9.0)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_slow_decays_carry_the_first_tokens_through_long_decoding(zoo, dtype):
+    """A unit whose a stays near one and retention heads with decays of 0.999 and 1: the first token still moves the
+    last logits after 260 tokens, 200 of them decoded one by one."""
+    config = M.layers_model([M.bare(M.chunked(1, 1, 16, 16, 16, 24, 2, 3)),
+                             M.bare(M.biased(1, 1, 16, 16, 2, 8, 8, 16, (0.999, 1.0), scale=0.01))], pairs=None)
+    folder, requests, want = zoo(config, dtype, [260], edit=_remember, key="remember")
+    tokens = requests["r0"]
+    moved = M.plain_logits(folder, [(tokens[0] + 1) % 97] + tokens[1:])[-1]
+    assert float((moved.float() - want["r0"][-1]).abs().max()) > 1e-3      # the plain model itself remembers
+    plans = dict(PLANS, long_decoding=lambda r: H.plan_bulk_then_single(r, tail=200))
+    for plan_name, plan in plans.items():
+        steps = plan(requests)
+        runner = make_runner(folder, dtype, 16, steps)
+        M.assert_close(H.run_plan(runner, steps), want, dtype, f"slow decays, {plan_name}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_large_pair_table_shows_a_lost_previous_token(zoo, dtype):
+    def edit(tensors):
+        tensors["bigram"] = (tensors["bigram"].float() * 10.0).to(tensors["bigram"].dtype)
+
+    config = M.layers_model([M.dense(M.chunked(1, 1, 16, 16, 64, 8, 1, 1), 24)], pairs=(29, 5, 3))
+    folder, requests, want = zoo(config, dtype, [60, 31, 17], edit=edit, key="pairs")
+    lost = M.plain_logits(folder, requests["r0"], edit=lambda c: c["embedding"]["bigram"].update(mul_prev=0))
+    assert float((lost.float() - want["r0"]).abs().max()) > 0.5
+    for plan_name, plan in PLANS.items():
+        steps = plan(requests)
+        runner = make_runner(folder, dtype, 8, steps)
+        M.assert_close(H.run_plan(runner, steps), want, dtype, f"pair table, {plan_name}", 0.0)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_of_a_repeating_shape_are_recorded_and_replayed(zoo, dtype):
+    """Portions of 300 tokens with two wanted rows: from its third occurrence the step is a recorded one (the portion
+    list, the experts' work lists, the slots of the states and of the carried tokens are all read on the device at
+    replay), with the bits of an unrecorded step."""
+    config, page = M.MODELS["U"]
+    folder, requests, want = zoo(config, dtype, [900, 900, 601], key="recorded")
+    steps = []
+    for uid, toks in requests.items():
+        for i in range(0, len(toks) - 1, 300):
+            n = min(300, len(toks) - i)
+            steps.append({"entries": [(uid, toks[i:i + n], [n - 1, 0])], "end": [uid] if i + n == len(toks) else []})
+    steps.append({"entries": [("r2", requests["r2"][600:601], [0])], "end": ["r2"]})
+    runner = make_runner(folder, dtype, page, steps, max_live=2)
+    rows = H.run_plan(runner, steps)
+    assert runner.graphs is not None and runner.graphs.mixed_replays >= 4
+    M.assert_close(rows, want, dtype, "recorded steps of 300 tokens")
+    fresh = make_runner(folder, dtype, page, steps, max_live=2, use_graphs=False)
+    plain_rows = H.run_plan(fresh, steps)
+    for key, row in rows.items():
+        assert torch.equal(row, plain_rows[key]), key
+
+
+# ---------------------------------------------------------------------------
+# the entry point, the scheduler, the command line, the trace runner
+# ---------------------------------------------------------------------------
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generation_through_the_engine(tmp_path, dtype):
+    from lockstep_b200 import Engine, Request
+
+    config, page = M.MODELS["S"]
+    folder = M.make_folder(tmp_path, config, seed=21, dtype=dtype)
+    engine = Engine(folder, dtype=dtype, num_pages=64, page_size=page, max_running=12, max_step_tokens=96,
+                    max_seq_len=512)
+    prompts = {f"g{i}": H.random_tokens(n, config["vocab"], seed=300 + i)
+               for i, n in enumerate([33, 7, 120, 1, 64, 18, 45, 2, 90, 11])}
+    got = engine.generate([Request(uid=u, prompt=p, max_new_tokens=8) for u, p in prompts.items()])
+    wrong = []
+    for uid, prompt in prompts.items():
+        assert len(got[uid]) == 8
+        rows = M.plain_logits(folder, list(prompt) + got[uid])     # causal: one pass gives every step's logits
+        for i, tok in enumerate(got[uid]):
+            row = rows[len(prompt) + i - 1]
+            margin = 2 * M.TOLERANCE[dtype] * (1 + float(row.abs().max()))
+            if not float(row[tok]) >= float(row.max()) - margin:
+                wrong.append((uid, i, tok))
+    assert len(wrong) <= int(M.CLOSE_CALLS[dtype] * 80), (dtype, wrong)
+    assert engine.runner.graphs is not None and engine.runner.graphs.replays > 0
+    engine.cache.audit()
+    assert engine.cache.live == 0
+
+
+def test_the_command_line_writes_a_random_model_and_runs_a_workload(tmp_path):
+    config, page = M.MODELS["U"]
+    (tmp_path / "config.json").write_text(json.dumps(config))
+    folder = tmp_path / "model"
+    lockstep = [sys.executable, str(ROOT / "bin" / "lockstep")]
+    proc = subprocess.run(lockstep + ["random-model", "--config", str(tmp_path / "config.json"), "--out", str(folder),
+                                      "--seed", "5", "--init-std", "0.15", "--gain-std", "0.1"],
+                          capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    prompts = {f"c{i}": H.random_tokens(n, config["vocab"], 95 + i) for i, n in enumerate([4, 23, 50])}
+    workload = tmp_path / "workload.json"
+    requests = [{"uid": u, "prompt": p, "max_new_tokens": 10} for u, p in prompts.items()]
+    requests += [{"uid": "s0", "prompt": prompts["c1"], "max_new_tokens": 12, "temperature": 0.8, "top_p": 0.9, "seed": 3}]
+    workload.write_text(json.dumps(requests))
+    proc = subprocess.run(lockstep + ["run", "--model", str(folder), "--dtype", "float32", "--workload", str(workload),
+                                      "--policy", "fixed-chunk:16", "--num-blocks", "40", "--block-size", str(page),
+                                      "--max-running", "3"], capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    lines = {l["uid"]: l for l in (json.loads(x) for x in proc.stdout.splitlines() if x.startswith("{"))}
+    assert set(lines) == set(prompts) | {"s0"}
+    for uid, prompt in prompts.items():
+        got = lines[uid]["generated"]
+        assert len(got) == 10
+        rows = M.plain_logits(folder, list(prompt) + got)
+        for i, tok in enumerate(got):
+            row = rows[len(prompt) + i - 1]
+            assert float(row[tok]) >= float(row.max()) - 2 * M.TOLERANCE["float32"] * (1 + float(row.abs().max()))
+    assert len(lines["s0"]["generated"]) == 12 and all(0 <= t < config["vocab"] for t in lines["s0"]["generated"])
+
+
+def test_trace_runner_replays_a_trace(tmp_path):
+    config, page = M.MODELS["T"]
+    folder = M.make_folder(tmp_path, config, seed=9, dtype="bfloat16")
+    requests = {f"t{i}": H.random_tokens(n, config["vocab"], seed=70 + i) for i, n in enumerate([40, 130, 25, 61, 90])}
+    steps = H.plan_mixed(requests, max_live=4)
+    out = tmp_path / "out"
+    for dtype in ("bfloat16", "float32"):
+        proc = subprocess.run([sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(folder), "--dtype", dtype,
+                               "--out", str(out / dtype), "--max-tokens", str(H.max_live_tokens(steps, 64))],
+                              input=H.plan_to_jsonl(steps), capture_output=True, text=True, timeout=900)
+        assert proc.returncode == 0, proc.stderr[-2000:]
+        assert [l for l in proc.stdout.splitlines() if l.startswith("done ")] == [f"done {i}" for i in range(len(steps))]
+        want = {u: M.plain_logits(folder, t).float() for u, t in requests.items()}
+        at = {u: 0 for u in requests}
+        rows = {}
+        for i, step in enumerate(steps):
+            got = np.fromfile(out / dtype / f"{i}.f32", dtype="<f4").reshape(-1, config["vocab"])
+            r = 0
+            for uid, toks, wanted in step["entries"]:
+                for wpos in wanted:
+                    rows[(uid, at[uid] + wpos)] = torch.from_numpy(got[r].copy())
+                    r += 1
+                at[uid] += len(toks)
+            assert r == got.shape[0]
+        M.assert_close(rows, want, dtype, f"trace runner, {dtype}")
