@@ -8,55 +8,82 @@
 //     token and the one before it, whose last row serves a sequence's first token;
 //   - float32 rows written into some columns of a wider row of the engine's type; logits times a
 //     factor, then capped with tanh.
-// All reductions run in float32 in an order fixed by the row's own width (a lane's elements
-// ascending, the lanes by an xor tree), so a row's result does not depend on the batch.
+// All reductions run in float32 in an order fixed by the row's own width (a thread's elements
+// ascending, the lanes by an xor tree, the warps ascending), so a row's result does not depend on the batch.
 #include "common.cuh"
 
 namespace {
 
-constexpr int ROW_WARPS = 4;      // rows of one block: a warp per row
+constexpr int ROW_THREADS = 256;  // a block per row
 
 template <typename TG>
 __device__ __forceinline__ float gain_of(const TG* g, int i) { return ls_to_float<TG>(g[i]); }
 
-// (x - mean) rsqrt(var + eps) gain over float32 rows
+// Sum over the block in a fixed order (lanes by xor tree, warps ascending); every thread gets it.  `scratch`: 32 floats.
+__device__ __forceinline__ float row_sum(float v, float* scratch) {
+  const float total = ls_block_sum(v, scratch);
+  __syncthreads();                 // scratch is free for the next sum
+  return total;
+}
+
+// (x - mean) rsqrt(var + eps) gain over float32 rows.  A thread takes the elements tid, tid + 256, ... of the row and
+// keeps up to eight of them in registers between the passes (rows up to 2,048 wide are read once).
 template <typename TG, typename TO>
-__global__ void __launch_bounds__(ROW_WARPS * 32)
+__global__ void __launch_bounds__(ROW_THREADS)
 layernorm_kernel(const float* __restrict__ x, const int* __restrict__ row_index, const TG* __restrict__ gain,
                  TO* __restrict__ out, int rows, int width, int x_rows, float eps, int* err) {
+  __shared__ float scratch[32];
   ls_dependency_sync();
-  const int r = blockIdx.x * ROW_WARPS + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-  if (r >= rows) return;
+  const int r = blockIdx.x, tid = threadIdx.x;
   int src_row = r;
   if (row_index != nullptr) {
     src_row = row_index[r];
     if (src_row < 0 || src_row >= x_rows) {
-      if (lane == 0) ls_record_fault(err, LS_DEV_ROW_RANGE, r);
+      if (tid == 0) ls_record_fault(err, LS_DEV_ROW_RANGE, r);
       src_row = 0;
     }
   }
   const float* row = x + (int64_t)src_row * width;
+  constexpr int KEEP = 8;
+  float v[KEEP];
+#pragma unroll
+  for (int j = 0; j < KEEP; ++j) v[j] = tid + j * ROW_THREADS < width ? row[tid + j * ROW_THREADS] : 0.f;
   float s = 0.f;
-  for (int i = lane; i < width; i += 32) s += row[i];
-  const float mean = ls_warp_sum(s) / (float)width;
+#pragma unroll
+  for (int j = 0; j < KEEP; ++j) s += v[j];
+  for (int i = tid + KEEP * ROW_THREADS; i < width; i += ROW_THREADS) s += row[i];
+  const float mean = row_sum(s, scratch) / (float)width;
   float q = 0.f;
-  for (int i = lane; i < width; i += 32) {
+#pragma unroll
+  for (int j = 0; j < KEEP; ++j) {
+    const float d = tid + j * ROW_THREADS < width ? v[j] - mean : 0.f;
+    q = fmaf(d, d, q);
+  }
+  for (int i = tid + KEEP * ROW_THREADS; i < width; i += ROW_THREADS) {
     const float d = row[i] - mean;
     q = fmaf(d, d, q);
   }
-  const float rstd = 1.0f / sqrtf(ls_warp_sum(q) / (float)width + eps);
+  const float rstd = 1.0f / sqrtf(row_sum(q, scratch) / (float)width + eps);
   TO* dst = out + (int64_t)r * width;
-  for (int i = lane; i < width; i += 32) dst[i] = ls_from_float<TO>((row[i] - mean) * rstd * gain_of<TG>(gain, i));
+#pragma unroll
+  for (int j = 0; j < KEEP; ++j) {
+    const int i = tid + j * ROW_THREADS;
+    if (i < width) dst[i] = ls_from_float<TO>((v[j] - mean) * rstd * gain_of<TG>(gain, i));
+  }
+  for (int i = tid + KEEP * ROW_THREADS; i < width; i += ROW_THREADS)
+    dst[i] = ls_from_float<TO>((row[i] - mean) * rstd * gain_of<TG>(gain, i));
 }
 
-// residual += post(scale sum_b rms_b(x_b) gain_b), post = layer norm with post_gain, or nothing
-__global__ void __launch_bounds__(ROW_WARPS * 32)
+// residual += post(scale sum_b rms_b(x_b) gain_b), post = layer norm with post_gain, or nothing.  The merged row
+// lies in shared memory between the passes.
+__global__ void __launch_bounds__(ROW_THREADS)
 norm_merge_add_kernel(float* __restrict__ residual, const float* __restrict__ branches, int n, int64_t branch_stride,
                       const float* __restrict__ branch_gain, float scale, const float* __restrict__ post_gain,
                       int rows, int width, float eps_branch, float eps_post) {
+  extern __shared__ float merged[];                 // [width]
+  __shared__ float scratch[32];
   ls_dependency_sync();
-  const int r = blockIdx.x * ROW_WARPS + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-  if (r >= rows) return;
+  const int r = blockIdx.x, tid = threadIdx.x;
   constexpr int MAX_N = 4;
   float rstd_b[MAX_N];
 #pragma unroll
@@ -65,11 +92,14 @@ norm_merge_add_kernel(float* __restrict__ residual, const float* __restrict__ br
     if (b < n && branch_gain != nullptr) {
       const float* row = branches + b * branch_stride + (int64_t)r * width;
       float q = 0.f;
-      for (int i = lane; i < width; i += 32) q = fmaf(row[i], row[i], q);
-      rstd_b[b] = 1.0f / sqrtf(ls_warp_sum(q) / (float)width + eps_branch);
+#pragma unroll 4
+      for (int i = tid; i < width; i += ROW_THREADS) q = fmaf(row[i], row[i], q);
+      rstd_b[b] = 1.0f / sqrtf(row_sum(q, scratch) / (float)width + eps_branch);
     }
   }
-  auto merged = [&](int i) {
+  float s = 0.f;
+#pragma unroll 2
+  for (int i = tid; i < width; i += ROW_THREADS) {
     float v = 0.f;
 #pragma unroll
     for (int b = 0; b < MAX_N; ++b)
@@ -77,26 +107,28 @@ norm_merge_add_kernel(float* __restrict__ residual, const float* __restrict__ br
         const float xb = branches[b * branch_stride + (int64_t)r * width + i];
         v += branch_gain != nullptr ? xb * rstd_b[b] * branch_gain[b * width + i] : xb;
       }
-    return v * scale;
-  };
+    v *= scale;
+    merged[i] = v;                                  // (read back by this thread alone)
+    s += v;
+  }
   float* dst = residual + (int64_t)r * width;
   if (post_gain == nullptr) {
-    for (int i = lane; i < width; i += 32) dst[i] += merged(i);
+#pragma unroll 4
+    for (int i = tid; i < width; i += ROW_THREADS) dst[i] += merged[i];
     return;
   }
-  float s = 0.f;
-  for (int i = lane; i < width; i += 32) s += merged(i);
-  const float mean = ls_warp_sum(s) / (float)width;
+  const float mean = row_sum(s, scratch) / (float)width;
   float q = 0.f;
-  for (int i = lane; i < width; i += 32) {
-    const float d = merged(i) - mean;
+  for (int i = tid; i < width; i += ROW_THREADS) {
+    const float d = merged[i] - mean;
     q = fmaf(d, d, q);
   }
-  const float rstd = 1.0f / sqrtf(ls_warp_sum(q) / (float)width + eps_post);
-  for (int i = lane; i < width; i += 32) dst[i] += (merged(i) - mean) * rstd * post_gain[i];
+  const float rstd = 1.0f / sqrtf(row_sum(q, scratch) / (float)width + eps_post);
+#pragma unroll 4
+  for (int i = tid; i < width; i += ROW_THREADS) dst[i] += (merged[i] - mean) * rstd * post_gain[i];
 }
 
-// out[t] = table[id] factor + pairs[row(previous id, id)]; also a copy in the engine's type into `copy`
+// out[t] = table[id] factor + pairs[row(previous id, id)]
 template <typename T>
 __global__ void pair_embed_kernel(const int* __restrict__ ids, const int* __restrict__ token_slot,
                                   const int* __restrict__ carried, int64_t carried_stride, const T* __restrict__ table,
@@ -163,7 +195,7 @@ LS_API int ls_layernorm(const float* x, const int* row_index, const void* gain, 
                         int rows, int width, int x_rows, float eps, int* err, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (width <= 0) return LS_E_SIZE;
-  const dim3 grid((rows + ROW_WARPS - 1) / ROW_WARPS), block(ROW_WARPS * 32);
+  const dim3 grid(rows), block(ROW_THREADS);
   LS_COUNT(LS_K_LAYERNORM);
 #define LS_LN(TG, TO) \
   ls_launch(layernorm_kernel<TG, TO>, grid, block, 0, stream, x, row_index, (const TG*)gain, (TO*)out, rows, width, x_rows, eps, err)
@@ -181,8 +213,16 @@ LS_API int ls_norm_merge_add(float* residual, const float* branches, int n, long
                              cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (width <= 0 || n < 1 || n > 4) return LS_E_SIZE;
+  const size_t smem = sizeof(float) * (size_t)width;
+  if (smem > 200 * 1024) return LS_E_SMEM;
+  static size_t configured = 48 * 1024;
+  if (smem > configured) {
+    if (cudaFuncSetAttribute(norm_merge_add_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      return LS_E_SMEM;
+    configured = smem;
+  }
   LS_COUNT(LS_K_NORM_MERGE_ADD);
-  ls_launch(norm_merge_add_kernel, dim3((rows + ROW_WARPS - 1) / ROW_WARPS), dim3(ROW_WARPS * 32), 0, stream, residual, branches,
+  ls_launch(norm_merge_add_kernel, dim3(rows), dim3(ROW_THREADS), smem, stream, residual, branches,
             n, (int64_t)branch_stride, branch_gain, scale, post_gain, rows, width, eps_branch, eps_post);
   return ls_launch_status();
 }

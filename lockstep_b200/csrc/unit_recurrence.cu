@@ -11,13 +11,15 @@
 // unit_scan walks every portion token by token, one thread a channel, writes S gelu(y) in the
 // engine's type, and keeps S and the last taps - 1 inputs of the convolution in the slot
 // (float32 [width + (taps - 1) width], the inputs oldest first).
-// A token's arithmetic does not depend on the portion it arrives in: the gates' sums run over
-// ascending input channels with one accumulator each, the walk is one fused multiply-add a token.
+// A token's arithmetic does not depend on the portion it arrives in: a gate's sum is four chains over
+// ascending quarters of the input channels, added in ascending order; the walk is one fused multiply-add a token.
 #include "common.cuh"
 
 namespace {
 
-constexpr int GATE_TOKENS = 8;      // tokens of one block of unit_gates
+constexpr int GATE_TOKENS = 16;     // tokens of one block of unit_gates
+constexpr int GATE_COLS = 32;       // output channels of one block
+constexpr int GATE_THREADS = 128;   // four warps: a quarter of the input channels each
 constexpr int MAX_UNIT_TAPS = 8;
 
 struct GateArgs {
@@ -38,63 +40,105 @@ struct GateArgs {
   float* a_out;            // [T, width]
   float* b_out;
   int T, width, blocks, taps;
+  int runs;                // runs of GATE_COLS output channels that one block takes, one after the other
   float c;                 // the factor in log a
 };
 
+// A block: GATE_TOKENS tokens, one part, some runs of GATE_COLS output channels of it (all of them in a step of many
+// tokens, where staging the convolution once pays; one run in a step of few, where more blocks do); its four warps
+// each take a quarter of the input channels (ascending, one accumulator a token and matrix), the quarters are added
+// in ascending order.
 template <typename T>
-__global__ void __launch_bounds__(256) unit_gates_kernel(GateArgs g) {
-  extern __shared__ float us[];                 // [GATE_TOKENS][bw]
+__global__ void __launch_bounds__(GATE_THREADS) unit_gates_kernel(GateArgs g) {
+  extern __shared__ __align__(16) float us[];   // u [bw][GATE_TOKENS], then the quarters' sums [4][2][GATE_TOKENS][GATE_COLS]
   ls_dependency_sync();
   const int bw = g.width / g.blocks, part = blockIdx.y, t0 = blockIdx.x * GATE_TOKENS;
   const int nt = g.T - t0 < GATE_TOKENS ? g.T - t0 : GATE_TOKENS;
   const T* proj = reinterpret_cast<const T*>(g.proj);
-  // the convolution: channel c of token t reads its own input and the taps - 1 before it
-  for (int e = threadIdx.x; e < nt * bw; e += blockDim.x) {
-    const int tt = e / bw, k = e - tt * bw, c = part * bw + k, t = t0 + tt;
-    const int slot = g.token_slot[t];
-    // how many of the tokens in front of t belong to its portion (up to taps - 1)
-    int inside = 0;
-    while (inside < g.taps - 1 && t - inside - 1 >= 0 && g.token_slot[t - inside - 1] == slot) ++inside;
-    const float* carried = g.state + (int64_t)slot * g.state_stride + g.width;
-    float acc = g.conv_b[c];
-    for (int j = 0; j < g.taps; ++j) {
-      const int back = g.taps - 1 - j;           // tap j reads the input `back` tokens ago
-      float x;
-      if (back <= inside) x = ls_to_float<T>(proj[(int64_t)(t - back) * g.ld + g.x_at + c]) + g.x_bias[c];
-      else x = carried[(int64_t)(g.taps - 1 + inside - back) * g.width + c];
-      acc = fmaf(g.conv_w[(int64_t)c * g.taps + j], x, acc);
+  float* sums = us + bw * GATE_TOKENS;
+  __shared__ int tok_slot[GATE_TOKENS], tok_inside[GATE_TOKENS];
+  if (threadIdx.x < GATE_TOKENS) {
+    const int t = t0 + threadIdx.x;
+    int slot = 0, inside = 0;
+    if (threadIdx.x < nt) {
+      slot = g.token_slot[t];
+      // how many of the tokens in front of t belong to its portion (up to taps - 1)
+      while (inside < g.taps - 1 && t - inside - 1 >= 0 && g.token_slot[t - inside - 1] == slot) ++inside;
     }
-    us[tt * bw + k] = acc;
+    tok_slot[threadIdx.x] = slot;
+    tok_inside[threadIdx.x] = inside;
   }
   __syncthreads();
+  // the convolution: channel c of token t reads its own input and the taps - 1 before it
+  for (int e = threadIdx.x; e < GATE_TOKENS * bw; e += blockDim.x) {
+    const int tt = e / bw, k = e - tt * bw, c = part * bw + k, t = t0 + tt;
+    float acc = 0.f;
+    if (tt < nt) {
+      const int inside = tok_inside[tt];
+      const float* carried = g.state + (int64_t)tok_slot[tt] * g.state_stride + g.width;
+      acc = g.conv_b[c];
+      for (int j = 0; j < g.taps; ++j) {
+        const int back = g.taps - 1 - j;           // tap j reads the input `back` tokens ago
+        float x;
+        if (back <= inside) x = ls_to_float<T>(proj[(int64_t)(t - back) * g.ld + g.x_at + c]) + g.x_bias[c];
+        else x = carried[(int64_t)(g.taps - 1 + inside - back) * g.width + c];
+        acc = fmaf(g.conv_w[(int64_t)c * g.taps + j], x, acc);
+      }
+    }
+    us[k * GATE_TOKENS + tt] = acc;
+  }
+  __syncthreads();
+  const int lane = threadIdx.x & 31, quarter = threadIdx.x >> 5;
+  const int per = (bw + 3) / 4, k_lo = quarter * per, k_hi = k_lo + per < bw ? k_lo + per : bw;
   const T* w_r = reinterpret_cast<const T*>(g.w_r) + (int64_t)part * bw * bw;
   const T* w_i = reinterpret_cast<const T*>(g.w_i) + (int64_t)part * bw * bw;
-  for (int j = threadIdx.x; j < bw; j += blockDim.x) {
+  // the block's runs of GATE_COLS output channels, one after the other
+  for (int run = blockIdx.z * g.runs; run < (blockIdx.z + 1) * g.runs && run * GATE_COLS < bw; ++run) {
+    const int j = run * GATE_COLS + lane;
     float ar[GATE_TOKENS], ai[GATE_TOKENS];
 #pragma unroll
     for (int tt = 0; tt < GATE_TOKENS; ++tt) ar[tt] = ai[tt] = 0.f;
-    for (int k = 0; k < bw; ++k) {
-      const float wr = ls_to_float<T>(w_r[(int64_t)k * bw + j]), wi = ls_to_float<T>(w_i[(int64_t)k * bw + j]);
+    if (j < bw) {
+#pragma unroll 4
+      for (int k = k_lo; k < k_hi; ++k) {
+        const float wr = ls_to_float<T>(w_r[(int64_t)k * bw + j]), wi = ls_to_float<T>(w_i[(int64_t)k * bw + j]);
+        const float4* u4 = reinterpret_cast<const float4*>(us + k * GATE_TOKENS);
 #pragma unroll
-      for (int tt = 0; tt < GATE_TOKENS; ++tt) {
-        const float u = us[tt * bw + k];
-        ar[tt] = fmaf(wr, u, ar[tt]);
-        ai[tt] = fmaf(wi, u, ai[tt]);
+        for (int q = 0; q < GATE_TOKENS / 4; ++q) {
+          const float4 u = u4[q];
+          ar[4 * q] = fmaf(wr, u.x, ar[4 * q]); ai[4 * q] = fmaf(wi, u.x, ai[4 * q]);
+          ar[4 * q + 1] = fmaf(wr, u.y, ar[4 * q + 1]); ai[4 * q + 1] = fmaf(wi, u.y, ai[4 * q + 1]);
+          ar[4 * q + 2] = fmaf(wr, u.z, ar[4 * q + 2]); ai[4 * q + 2] = fmaf(wi, u.z, ai[4 * q + 2]);
+          ar[4 * q + 3] = fmaf(wr, u.w, ar[4 * q + 3]); ai[4 * q + 3] = fmaf(wi, u.w, ai[4 * q + 3]);
+        }
       }
     }
-    const int c = part * bw + j;
-    const float br = g.b_r[c], bi = g.b_i[c], rate = g.rate[c];
+    __syncthreads();                               // the run before is done with the quarters' sums
 #pragma unroll
     for (int tt = 0; tt < GATE_TOKENS; ++tt) {
-      if (tt >= nt) break;
-      const float r = 1.0f / (1.0f + expf(-(ar[tt] + br)));
-      const float i = 1.0f / (1.0f + expf(-(ai[tt] + bi)));
-      const float log_a = -g.c * r * rate;
-      const float a = expf(log_a);
-      // sqrt(1 - a^2) through expm1: a decay near one keeps its digits
-      const float in = sqrtf(-expm1f(2.0f * log_a)) * i * us[tt * bw + j];
-      g.a_out[(int64_t)(t0 + tt) * g.width + c] = a;
-      g.b_out[(int64_t)(t0 + tt) * g.width + c] = in;
+      sums[((quarter * 2 + 0) * GATE_TOKENS + tt) * GATE_COLS + lane] = ar[tt];
+      sums[((quarter * 2 + 1) * GATE_TOKENS + tt) * GATE_COLS + lane] = ai[tt];
+    }
+    __syncthreads();
+    if (j < bw) {
+      const int c = part * bw + j;
+      const float br = g.b_r[c], bi = g.b_i[c], rate = g.rate[c];
+      // warp `quarter` finishes the tokens quarter, quarter + 4, ...
+      for (int tt = quarter; tt < nt; tt += 4) {
+        float zr = 0.f, zi = 0.f;
+#pragma unroll
+        for (int qq = 0; qq < 4; ++qq) {
+          zr += sums[((qq * 2 + 0) * GATE_TOKENS + tt) * GATE_COLS + lane];
+          zi += sums[((qq * 2 + 1) * GATE_TOKENS + tt) * GATE_COLS + lane];
+        }
+        const float r = 1.0f / (1.0f + expf(-(zr + br)));
+        const float i = 1.0f / (1.0f + expf(-(zi + bi)));
+        const float log_a = -g.c * r * rate;
+        // sqrt(1 - a^2) through expm1: a decay near one keeps its digits
+        const float in = sqrtf(-expm1f(2.0f * log_a)) * i * us[j * GATE_TOKENS + tt];
+        g.a_out[(int64_t)(t0 + tt) * g.width + c] = expf(log_a);
+        g.b_out[(int64_t)(t0 + tt) * g.width + c] = in;
+      }
     }
   }
 }
@@ -219,14 +263,16 @@ LS_API int ls_unit_gates(const void* proj, long long ld, int x_at, int dtype, co
   if (tokens <= 0) return 0;
   if (width <= 0 || blocks <= 0 || width % blocks || taps < 1 || taps > MAX_UNIT_TAPS) return LS_E_SIZE;
   const int bw = width / blocks;
-  const size_t smem = sizeof(float) * (size_t)GATE_TOKENS * bw;
-  if (smem > 200 * 1024 || blocks > 65535) return LS_E_SMEM;
+  const size_t smem = sizeof(float) * ((size_t)GATE_TOKENS * bw + 4 * 2 * GATE_TOKENS * GATE_COLS);
+  if (smem > 200 * 1024 || blocks > 65535 || (bw + GATE_COLS - 1) / GATE_COLS > 65535) return LS_E_SMEM;
   GateArgs g;
   g.proj = proj; g.ld = ld; g.x_at = x_at; g.x_bias = x_bias; g.conv_w = conv_w; g.conv_b = conv_b; g.state = state;
   g.state_stride = state_stride; g.token_slot = token_slot; g.w_r = w_r; g.w_i = w_i; g.b_r = b_r; g.b_i = b_i; g.rate = rate;
   g.a_out = a_out; g.b_out = b_out; g.T = tokens; g.width = width; g.blocks = blocks; g.taps = taps; g.c = c;
-  const dim3 grid((tokens + GATE_TOKENS - 1) / GATE_TOKENS, blocks);
-  const int threads = bw >= 256 ? 256 : (bw + 31) / 32 * 32;
+  const int all_runs = (bw + GATE_COLS - 1) / GATE_COLS;
+  g.runs = tokens > 2 * GATE_TOKENS ? all_runs : 1;
+  const dim3 grid((tokens + GATE_TOKENS - 1) / GATE_TOKENS, blocks, (all_runs + g.runs - 1) / g.runs);
+  const int threads = GATE_THREADS;
   LS_COUNT(LS_K_UNIT_GATES);
   if (dtype == LS_F32) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(unit_gates_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
