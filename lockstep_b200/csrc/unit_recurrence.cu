@@ -270,15 +270,29 @@ LS_API int ls_unit_gates(const void* proj, long long ld, int x_at, int dtype, co
   g.state_stride = state_stride; g.token_slot = token_slot; g.w_r = w_r; g.w_i = w_i; g.b_r = b_r; g.b_i = b_i; g.rate = rate;
   g.a_out = a_out; g.b_out = b_out; g.T = tokens; g.width = width; g.blocks = blocks; g.taps = taps; g.c = c;
   const int all_runs = (bw + GATE_COLS - 1) / GATE_COLS;
+  const int tiles = (tokens + GATE_TOKENS - 1) / GATE_TOKENS;
   g.runs = tokens > 2 * GATE_TOKENS ? all_runs : 1;
+  // enough blocks for a few rounds over the device, so that the last round is not half empty
+  while (g.runs > 1 && (long long)tiles * blocks * ((all_runs + g.runs - 1) / g.runs) < 148LL * 6 * 3) g.runs = (g.runs + 1) / 2;
   const dim3 grid((tokens + GATE_TOKENS - 1) / GATE_TOKENS, blocks, (all_runs + g.runs - 1) / g.runs);
   const int threads = GATE_THREADS;
   LS_COUNT(LS_K_UNIT_GATES);
   if (dtype == LS_F32) {
-    if (smem > 48 * 1024) cudaFuncSetAttribute(unit_gates_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    // (the kernel has a little static shared memory besides: the limit is asked for from 40 KB on)
+    static size_t set_f32 = 40 * 1024;
+    if (smem > set_f32) {
+      if (cudaFuncSetAttribute(unit_gates_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        return LS_E_SMEM;
+      set_f32 = smem;
+    }
     ls_launch(unit_gates_kernel<float>, grid, dim3(threads), smem, stream, g);
   } else if (dtype == LS_BF16) {
-    if (smem > 48 * 1024) cudaFuncSetAttribute(unit_gates_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    static size_t set_bf16 = 40 * 1024;
+    if (smem > set_bf16) {
+      if (cudaFuncSetAttribute(unit_gates_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        return LS_E_SMEM;
+      set_bf16 = smem;
+    }
     ls_launch(unit_gates_kernel<__nv_bfloat16>, grid, dim3(threads), smem, stream, g);
   } else {
     return LS_E_DTYPE;

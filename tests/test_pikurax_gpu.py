@@ -127,7 +127,7 @@ def test_pair_embedding_carries_the_last_token(dtype):
 
 
 @pytest.mark.parametrize("dtype", [F32, BF16])
-@pytest.mark.parametrize("width, blocks, taps", [(40, 5, 4), (26, 2, 1), (13, 13, 3), (320, 1, 2), (96, 3, 8)])
+@pytest.mark.parametrize("width, blocks, taps", [(40, 5, 4), (26, 2, 1), (13, 13, 3), (320, 1, 2), (96, 3, 8), (1280, 2, 2)])
 def test_recurrent_unit_across_calls(dtype, width, blocks, taps):
     """Gates, decays and the walk of the unit for three requests in portions across calls (one of a single token, one
     shorter than the convolution), against the plain functions on the whole sequences; lam so negative that S keeps
@@ -416,17 +416,20 @@ def test_sharp_softmax_at_the_edges_of_chunks(zoo, chunk, dim, pad, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_sharp_biased_attention_reaches_far_keys_and_its_sink(zoo, dtype):
+@pytest.mark.parametrize("dim, vdim", [(32, 16), (64, 64)])
+def test_sharp_biased_attention_reaches_far_keys_and_its_sink(zoo, dim, vdim, dtype):
     """Large queries against a weak distance bias: rows whose largest key lies hundreds of tokens back, rows the sink
     takes and rows it does not; a model without the sink, the cap or the temperature gives other logits."""
-    config = M.layers_model([M.bare(M.biased(4, 2, 32, 16, 2, 8, 8, 8, (0.9, 0.99), q_temp=(0.6, 32), softcap=30.0, scale=0.5))],
-                            width=64)
+    from lockstep_b200 import kernels as K
+
+    config = M.layers_model([M.bare(M.biased(4, 2, dim, vdim, 2, 8, 8, 8, (0.9, 0.99), q_temp=(0.6, 32), softcap=30.0,
+                                             scale=0.5 * (32 / dim) ** 0.5))], width=64)
 
     def edit(tensors):
         _sharpen(2.0)(tensors)
         tensors["l0.mix.left.sink"] = torch.tensor([9.0, 14.0, 2.0, -3.0]).to(tensors["l0.mix.left.sink"].dtype)
 
-    folder, requests, want = zoo(config, dtype, [500, 61], edit=edit, key="sharp-biased")
+    folder, requests, want = zoo(config, dtype, [500, 61], edit=edit, key=f"sharp-biased-{dim}")
     from safetensors.torch import load_file
     w = {k: v.double() for k, v in load_file(str(folder / "model.safetensors")).items()}
     x = plain.layer_norm(plain.embedding(requests["r0"], w, config), w["l0.norm1"], 1e-5)
@@ -439,11 +442,16 @@ def test_sharp_biased_attention_reaches_far_keys_and_its_sink(zoo, dtype):
     for change in (lambda m: m.pop("softcap"), lambda m: m.pop("q_temp")):
         other = M.plain_logits(folder, requests["r0"], edit=lambda c: change(c["layers"][0]["mixer"]["left"]))
         assert float((other.float() - want["r0"]).abs().max()) > 0.5
+    before = K.kernel_counts()
     for plan_name, plan in PLANS.items():
         steps = plan(requests)
         runner = make_runner(folder, dtype, 16, steps)
         M.assert_close(H.run_plan(runner, steps), want, dtype, f"sharp biased attention, {plan_name}", 0.0,
                        slack=1.0 if dtype == "float32" else 2.0)
+    after = K.kernel_counts()
+    # heads of 64 in bfloat16: prompt portions on the tensor cores (bias, cap and sink inside the kernel)
+    tensor_cores = after.get("attention_prefill_tc", 0) - before.get("attention_prefill_tc", 0)
+    assert (tensor_cores > 0) == (dtype == "bfloat16" and dim == 64)
 
 
 def _remember(tensors):
