@@ -50,7 +50,8 @@ struct GateArgs {
 // in ascending order.
 template <typename T>
 __global__ void __launch_bounds__(GATE_THREADS) unit_gates_kernel(GateArgs g) {
-  extern __shared__ __align__(16) float us[];   // u [bw][GATE_TOKENS], then the quarters' sums [4][2][GATE_TOKENS][GATE_COLS]
+  // u [bw][GATE_TOKENS], then the quarters' sums [4][2][GATE_TOKENS][GATE_COLS] (before them, there: the tile's inputs)
+  extern __shared__ __align__(16) float us[];
   ls_dependency_sync();
   const int bw = g.width / g.blocks, part = blockIdx.y, t0 = blockIdx.x * GATE_TOKENS;
   const int nt = g.T - t0 < GATE_TOKENS ? g.T - t0 : GATE_TOKENS;
@@ -69,19 +70,31 @@ __global__ void __launch_bounds__(GATE_THREADS) unit_gates_kernel(GateArgs g) {
     tok_inside[threadIdx.x] = inside;
   }
   __syncthreads();
-  // the convolution: channel c of token t reads its own input and the taps - 1 before it
+  // the inputs (with their bias) of the tile's tokens and of the taps - 1 tokens in front of them, where the quarters'
+  // sums will lie later: row r is token t0 - (taps - 1) + r.  Loads that do not wait for one another.
+  const int lead = g.taps - 1;
+  float* xs = sums;
+#pragma unroll 4
+  for (int e = threadIdx.x; e < (GATE_TOKENS + lead) * bw; e += blockDim.x) {
+    const int r = e / bw, k = e - r * bw, t = t0 - lead + r;
+    float x = 0.f;
+    if (t >= 0 && t < g.T) x = ls_to_float<T>(proj[(int64_t)t * g.ld + g.x_at + part * bw + k]) + g.x_bias[part * bw + k];
+    xs[e] = x;
+  }
+  __syncthreads();
+  // the convolution: channel c of token t reads its own input and the taps - 1 before it (those in front of the
+  // token's portion from the request's slot)
   for (int e = threadIdx.x; e < GATE_TOKENS * bw; e += blockDim.x) {
-    const int tt = e / bw, k = e - tt * bw, c = part * bw + k, t = t0 + tt;
+    const int tt = e / bw, k = e - tt * bw, c = part * bw + k;
     float acc = 0.f;
     if (tt < nt) {
       const int inside = tok_inside[tt];
       const float* carried = g.state + (int64_t)tok_slot[tt] * g.state_stride + g.width;
       acc = g.conv_b[c];
       for (int j = 0; j < g.taps; ++j) {
-        const int back = g.taps - 1 - j;           // tap j reads the input `back` tokens ago
-        float x;
-        if (back <= inside) x = ls_to_float<T>(proj[(int64_t)(t - back) * g.ld + g.x_at + c]) + g.x_bias[c];
-        else x = carried[(int64_t)(g.taps - 1 + inside - back) * g.width + c];
+        const int back = lead - j;                 // tap j reads the input `back` tokens ago
+        const float x = back <= inside ? xs[(lead + tt - back) * bw + k]
+                                       : carried[(int64_t)(lead + inside - back) * g.width + c];
         acc = fmaf(g.conv_w[(int64_t)c * g.taps + j], x, acc);
       }
     }
@@ -263,17 +276,15 @@ LS_API int ls_unit_gates(const void* proj, long long ld, int x_at, int dtype, co
   if (tokens <= 0) return 0;
   if (width <= 0 || blocks <= 0 || width % blocks || taps < 1 || taps > MAX_UNIT_TAPS) return LS_E_SIZE;
   const int bw = width / blocks;
-  const size_t smem = sizeof(float) * ((size_t)GATE_TOKENS * bw + 4 * 2 * GATE_TOKENS * GATE_COLS);
+  const size_t quarters = 4 * 2 * GATE_TOKENS * GATE_COLS, inputs = (size_t)(GATE_TOKENS + taps - 1) * bw;
+  const size_t smem = sizeof(float) * ((size_t)GATE_TOKENS * bw + (quarters > inputs ? quarters : inputs));
   if (smem > 200 * 1024 || blocks > 65535 || (bw + GATE_COLS - 1) / GATE_COLS > 65535) return LS_E_SMEM;
   GateArgs g;
   g.proj = proj; g.ld = ld; g.x_at = x_at; g.x_bias = x_bias; g.conv_w = conv_w; g.conv_b = conv_b; g.state = state;
   g.state_stride = state_stride; g.token_slot = token_slot; g.w_r = w_r; g.w_i = w_i; g.b_r = b_r; g.b_i = b_i; g.rate = rate;
   g.a_out = a_out; g.b_out = b_out; g.T = tokens; g.width = width; g.blocks = blocks; g.taps = taps; g.c = c;
   const int all_runs = (bw + GATE_COLS - 1) / GATE_COLS;
-  const int tiles = (tokens + GATE_TOKENS - 1) / GATE_TOKENS;
   g.runs = tokens > 2 * GATE_TOKENS ? all_runs : 1;
-  // enough blocks for a few rounds over the device, so that the last round is not half empty
-  while (g.runs > 1 && (long long)tiles * blocks * ((all_runs + g.runs - 1) / g.runs) < 148LL * 6 * 3) g.runs = (g.runs + 1) / 2;
   const dim3 grid((tokens + GATE_TOKENS - 1) / GATE_TOKENS, blocks, (all_runs + g.runs - 1) / g.runs);
   const int threads = GATE_THREADS;
   LS_COUNT(LS_K_UNIT_GATES);
