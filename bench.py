@@ -1000,16 +1000,16 @@ def pikurax_config(z):
     moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]}, "router": {"experts": z["experts"], "top": z["top"]},
            "shared": {"ff": z["shared_ff"]}}
     left = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": 128, "vdim": 128, "scale": 128 ** -0.5}
-    one = {"left": dict(left, rot={"dims": 64, "base": 500000.0}, mask={"size": PIKURAX_CHUNK}),
+    one = {"left": dict(left, rot={"dims": 64, "base": 1000000.0}, mask={"size": PIKURAX_CHUNK}),
            "right": {"width": z["unit"], "blocks": z["blocks"], "conv": 4}}
     two = {"left": dict(left, q_temp={"coef": 0.1, "every": 1024}, softcap=30.0),
            "right": {"heads": z["linear_heads"], "dim": 128, "vdim": 128, "rot": {"dims": 64, "base": 1000000.0},
                      "decay": [1.0 - 2.0 ** (-5 - h) for h in range(z["linear_heads"])]}}
     kinds = [("parallel", one, dense), ("parallel_2", two, moe), ("parallel", one, moe), ("parallel_2", two, dense),
              ("parallel", one, moe), ("parallel_2", two, moe)]
-    return {"architecture": "Pikurax", "vocab": DESIGN_VOCAB, "width": z["width"], "norm": {"eps": 1e-6}, "max_positions": 4096,
-            "embedding": {"scale": 16.0, "bigram": {"buckets": 65521, "mul_prev": 127, "mul_cur": 17}},
-            "loop": {"start": 1, "stop": 3, "times": 2}, "logit_scale": 1.0, "logit_softcap": 30.0,
+    return {"architecture": "Pikurax", "vocab": DESIGN_VOCAB, "width": z["width"], "norm": {"eps": 1e-5}, "max_positions": 4096,
+            "embedding": {"scale": 8.0, "bigram": {"buckets": 65521, "mul_prev": 8191, "mul_cur": 131}},
+            "loop": {"start": 1, "stop": 3, "times": 2}, "logit_scale": 1.0, "logit_softcap": 50.0,
             "layers": [{"type": t, "mixer": json.loads(json.dumps(m)), "mlp": json.loads(json.dumps(f))} for t, m, f in kinds]}
 
 

@@ -75,10 +75,10 @@ PAGE_S = 16
 # T: heads the tensor-core attention takes (64 and 128), sizes the tensor-core products take, forty experts,
 # a loop from the first layer, a large pair table
 MODEL_T = model(128, 211, 3e-6, [
-    moe(chunked(4, 2, 64, 32, 96, 160, 4, 3, base=500000.0), 40, 4, 64, shared=96),
-    dense(biased(2, 1, 128, 128, 4, 32, 32, 64, (0.97, 0.98, 0.99, 0.999), q_temp=(0.5, 64), softcap=30.0), 256),
+    moe(chunked(6, 3, 64, 32, 80, 160, 8, 3, base=250000.0), 40, 4, 72, shared=104),
+    dense(biased(2, 1, 128, 128, 4, 32, 32, 64, (0.97, 0.98, 0.99, 0.999), q_temp=(0.5, 48), softcap=30.0), 256),
     moe(chunked(2, 2, 128, 64, 200, 128, 1, 5), 6, 6, 40),
-], loop=(0, 2, 2), pairs=(1009, 127, 17), scale=11.0)
+], loop=(0, 2, 2), pairs=(1009, 31, 7), scale=11.0)
 PAGE_T = 8
 
 # U: odd sizes everywhere: a width and a vocabulary that are no multiples of 8, heads of 10 and 12 elements,
