@@ -98,6 +98,50 @@ def layers_model(layers, width=48, vocab=97, eps=1e-5, **kw):
     return model(width, vocab, eps, list(layers), **kw)
 
 
+def random_config(seed: int) -> dict:
+    """A configuration drawn from a seed: widths of 128 to 512, three to seven layers of either kind in any order, heads
+    of 32 to 128 elements on one to four key heads, chunks of 48 to 384, units of one to eight parts and two to five
+    taps, retention heads of 16 to 64 key elements, any feed-forward, loops anywhere or none."""
+    import random
+
+    r = random.Random(seed)
+    width, vocab = r.choice([128, 192, 256, 320, 384, 512]), r.choice([257, 384, 500, 512, 1000])
+    layers = []
+    for _ in range(r.choice([3, 4, 5, 6, 7])):
+        kv = r.choice([1, 2, 4])
+        heads = kv * r.choice([1, 2, 4])
+        if r.random() < 0.6:
+            dim = r.choice([32, 48, 64, 96, 128])
+            parts = r.choice([1, 2, 4, 8])
+            layer = chunked(heads, kv, dim, r.choice([dim, dim // 2, 16]), r.choice([48, 64, 100, 128, 384]),
+                            parts * r.choice([16, 40, 64]), parts, r.choice([2, 3, 4, 5]), base=r.choice([1e4, 1e6, 2e5]),
+                            scale=r.choice([dim ** -0.5, 0.1, 0.2]))
+        else:
+            dim, vdim = r.choice([32, 64, 96, 128]), r.choice([32, 64, 96])
+            r_heads, r_dim = r.choice([2, 3, 4, 6]), r.choice([16, 32, 64])
+            layer = biased(heads, kv, dim, vdim, r_heads, r_dim, r.choice([r_dim, r_dim // 2]), r.choice([32, 64]),
+                           [1.0 - 2.0 ** -r.randint(3, 10) for _ in range(r_heads)],
+                           q_temp=r.choice([None, (0.3, 64), (0.1, 16)]), softcap=r.choice([None, 20.0, 50.0]),
+                           base=r.choice([1e4, 1e6]), scale=r.choice([dim ** -0.5, 0.1]))
+        kind = r.random()
+        if kind < 0.15:
+            layers.append(bare(layer))
+        elif kind < 0.45:
+            layers.append(dense(layer, r.choice([128, 256, 384])))
+        else:
+            experts = r.choice([4, 8, 12])
+            layers.append(moe(layer, experts, r.choice([1, 2, 3]), r.choice([32, 64, 96]),
+                              shared=r.choice([None, 64, 96, 128])))
+    loop = None
+    if r.random() < 0.75:
+        start = r.randrange(len(layers))
+        stop = r.randint(start + 1, len(layers))
+        loop = (start, stop, r.choice([1, 2, 3]))
+    return model(width, vocab, r.choice([1e-6, 1e-5]), layers, loop=loop,
+                 pairs=r.choice([None, (509, 31, 7), (4093, 257, 5)]), scale=r.choice([1.0, 8.0, 12.0]),
+                 logit_scale=r.choice([1.0, 2.5]), logit_softcap=r.choice([None, 25.0]))
+
+
 INIT_STD = 0.15
 
 

@@ -338,6 +338,23 @@ def test_whole_models_in_every_cutting(zoo, model, plan_name, dtype):
         assert runner.graphs.replays > 100               # decoded tokens ran as recorded steps
 
 
+@pytest.mark.parametrize("seed", [1, 4, 9])
+def test_configurations_drawn_from_a_seed(zoo, seed):
+    """Larger models of sizes nobody chose (see ``pikurax_models.random_config``) in float32: four requests of up to 330
+    tokens whole, and on three slots with portions of some beside single tokens of others, with the same bits."""
+    config = M.random_config(seed)
+    folder, requests, want = zoo(config, "float32", [90, 330, 41, 200], seed=seed, key=f"drawn-{seed}")
+    rows = {}
+    for plan_name in ("whole", "mixed"):
+        steps = PLANS[plan_name](requests)
+        runner = make_runner(folder, "float32", 16, steps)
+        rows[plan_name] = H.run_plan(runner, steps)
+        M.assert_close(rows[plan_name], want, "float32", f"drawn configuration {seed}, {plan_name}")
+        runner.cache.audit()
+    for key, row in rows["whole"].items():
+        assert torch.equal(row, rows["mixed"][key]), key
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_the_stream_after_every_layer_run(zoo, dtype):
     """The residual stream after every run of a layer (a looped layer counts each time) against the plain model's."""
