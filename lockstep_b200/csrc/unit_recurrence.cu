@@ -20,7 +20,7 @@ namespace {
 constexpr int GATE_TOKENS = 16;     // tokens of one block of unit_gates
 constexpr int GATE_COLS = 32;       // output channels of one block
 constexpr int GATE_THREADS = 128;   // four warps: a quarter of the input channels each
-constexpr int MAX_UNIT_TAPS = 8;
+constexpr int MAX_UNIT_TAPS = 16;
 
 struct GateArgs {
   const void* proj;        // [T, ld]: the x projection at column x_at

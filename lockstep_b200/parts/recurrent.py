@@ -272,8 +272,8 @@ class GatedRecurrentUnit(Mixer):
     def __init__(self, hidden_size, width, blocks, conv_taps, runtime: Runtime, rate: float = 8.0, names=None):
         if width % blocks:
             raise ValueError(f"gated_recurrent_unit: {blocks} parts do not divide {width} channels")
-        if not 1 <= conv_taps <= 8:
-            raise ValueError(f"a convolution of {conv_taps} taps is not supported (1 to 8)")
+        if not 1 <= conv_taps <= 16:
+            raise ValueError(f"a convolution of {conv_taps} taps is not supported (1 to 16)")
         self.w, self.C, self.blocks, self.taps = int(hidden_size), int(width), int(blocks), int(conv_taps)
         self.rate, self.rt = float(rate), runtime
         self.names = {"y": "y", "y_bias": "y.b", "x": "x", "x_bias": "x.b", "conv": "conv", "conv_bias": "conv.b",

@@ -127,7 +127,7 @@ def test_pair_embedding_carries_the_last_token(dtype):
 
 
 @pytest.mark.parametrize("dtype", [F32, BF16])
-@pytest.mark.parametrize("width, blocks, taps", [(40, 5, 4), (26, 2, 1), (13, 13, 3), (320, 1, 2), (96, 3, 8), (1280, 2, 2)])
+@pytest.mark.parametrize("width, blocks, taps", [(40, 5, 4), (26, 2, 1), (13, 13, 3), (320, 1, 2), (96, 3, 8), (48, 2, 16), (1280, 2, 2)])
 def test_recurrent_unit_across_calls(dtype, width, blocks, taps):
     """Gates, decays and the walk of the unit for three requests in portions across calls (one of a single token, one
     shorter than the convolution), against the plain functions on the whole sequences; lam so negative that S keeps
